@@ -1,7 +1,8 @@
 """Typed configurations, one class per architecture."""
 from .base import ConfigError, ModelConfig, key, read_config_json
+from .bolelix import BolelixConfig
 from .lopazen import LopazenConfig
 from .qwen3 import Qwen3Config
 from .susalorn import SusalornConfig
 
-__all__ = ["ConfigError", "LopazenConfig", "ModelConfig", "Qwen3Config", "SusalornConfig", "key", "read_config_json"]
+__all__ = ["BolelixConfig", "ConfigError", "LopazenConfig", "ModelConfig", "Qwen3Config", "SusalornConfig", "key", "read_config_json"]

@@ -6,6 +6,9 @@
 // An optional sink - a key without a value whose fixed score `sink` every query sees - adds
 // exp(sink) to the softmax denominator once per (token, head); -INFINITY switches it off.
 // `sinks`, if given, holds one such score per query head and takes the place of `sink`.
+// `keep_first` > 0 (with a window): the first keep_first positions of the sequence stay visible to
+// every later token at their true positions, beside the window.  `gate`, if given, holds one value
+// per token and query head (row stride `gate_stride`): the head's output is multiplied by its sigmoid.
 // It serves whole prompts, chunks and single decoded tokens alike, since each token
 // carries its own position and slot; the faster bfloat16 kernels in attention_bf16.cu
 // cover the common head sizes, this one covers everything and is the 32-bit path.
@@ -69,7 +72,8 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
                                          int n_q_heads, float scale, int window, int n_splits,
                                          int keys_per_split, float* __restrict__ part_acc,
                                          float* __restrict__ part_ml, float sink,
-                                         const float* __restrict__ sinks) {
+                                         const float* __restrict__ sinks, int keep_first,
+                                         const T* __restrict__ gate, int gate_stride) {
   __shared__ float q_s[kGenericMaxDim];
   __shared__ float p_s[kAttnThreads];
   __shared__ size_t voff_s[kAttnThreads];
@@ -83,21 +87,27 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
   const int pos = positions[t];
   const size_t part_index = ((size_t)t * n_q_heads + h) * n_splits + split;
 
-  int lo = 0, hi = -1;                          // keys [lo, hi]
+  int lo = 0, hi = -1;                          // keys [lo, hi] ...
+  int f_lo = 0, f_hi = -1;                      // ... and the kept first keys [f_lo, f_hi] before them
   if (pos >= 0) {
     lo = window > 0 ? max(0, pos - window + 1) : 0;
     hi = pos;
+    f_hi = min(keep_first, lo) - 1;
     if (n_splits > 1) {
       lo = max(lo, split * keys_per_split);
       hi = min(hi, (split + 1) * keys_per_split - 1);
+      f_lo = max(f_lo, split * keys_per_split);
+      f_hi = min(f_hi, (split + 1) * keys_per_split - 1);
     }
   }
+  const int n_first = max(0, f_hi - f_lo + 1);
+  const int total = n_first + max(0, hi - lo + 1);
 
   float acc[kGenericAcc];                       // dims tid, tid + 128, ... (those below d)
 #pragma unroll
   for (int a = 0; a < kGenericAcc; ++a) acc[a] = 0.f;
   float m = -INFINITY, l = 0.f;
-  if (hi >= lo) {
+  if (total > 0) {
     const int slot = token_slot[t];
     const int* table = cache.block_table + (size_t)slot * cache.table_stride;
     const T* qrow = q + (size_t)t * q_row_stride + (size_t)h * d;
@@ -105,21 +115,23 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
     __syncthreads();
     const T* kbase = (const T*)cache.k;
     const T* vbase = (const T*)cache.v;
-    for (int start = lo; start <= hi; start += kAttnThreads) {
-      const int j = start + tid;
+    for (int start = 0; start < total; start += kAttnThreads) {
+      const int x = start + tid;
+      const int j = x < n_first ? f_lo + x : lo + (x - n_first);
+      const bool seen = x < total;
       float s = -INFINITY;
-      if (j <= hi) {
+      if (seen) {
         const size_t off = page_offset(cache, table[j / EK_PAGE], kv_head, j);
         voff_s[tid] = off;
         s = dot_row<T>(kbase + off, q_s, d);
       }
       const float m_new = fmaxf(m, block_max(s, scratch));
-      const float p = j <= hi ? expf(s - m_new) : 0.f;
+      const float p = seen ? expf(s - m_new) : 0.f;
       p_s[tid] = p;
       const float alpha = expf(m - m_new);      // m = -inf on the first chunk: 0
       l = l * alpha + block_sum(p, scratch);    // the barriers inside also publish p_s, voff_s
       m = m_new;
-      const int n = min(kAttnThreads, hi - start + 1);
+      const int n = min(kAttnThreads, total - start);
 #pragma unroll
       for (int a = 0; a < kGenericAcc; ++a) {
         acc[a] *= alpha;
@@ -137,7 +149,8 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
     T* orow = out + ((size_t)t * n_q_heads + h) * d;
     // a sink: one more term exp(sink) in the denominator, with no value (-inf: none)
     if (sink > -INFINITY && l > 0.f) l += expf(sink - m);
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float inv = l > 0.f ? 1.f / l : 0.f;
+    if (gate != nullptr) inv *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)t * gate_stride + h])));
 #pragma unroll
     for (int a = 0; a < kGenericAcc; ++a)
       if (tid + a * kAttnThreads < d) orow[tid + a * kAttnThreads] = from_f<T>(acc[a] * inv);
@@ -158,7 +171,8 @@ template <typename T>
 __global__ void attention_combine_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
                                          const float* __restrict__ part_ml, int n_q_heads,
                                          int head_dim, int n_splits, float sink,
-                                         const float* __restrict__ sinks) {
+                                         const float* __restrict__ sinks, const T* __restrict__ gate,
+                                         int gate_stride) {
   if (sinks != nullptr) sink = sinks[blockIdx.y];
   const size_t th = (size_t)blockIdx.x * n_q_heads + blockIdx.y;
   const float* ml = part_ml + 2 * th * n_splits;
@@ -168,7 +182,8 @@ __global__ void attention_combine_kernel(T* __restrict__ out, const float* __res
   for (int s = 0; s < n_splits; ++s)
     if (ml[2 * s + 1] > 0.f) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
   if (sink > -INFINITY && l > 0.f) l += expf(sink - m);                 // the sink, counted once
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  float inv = l > 0.f ? 1.f / l : 0.f;
+  if (gate != nullptr) inv *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)blockIdx.x * gate_stride + blockIdx.y])));
   for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < n_splits; ++s)
@@ -183,7 +198,8 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
                   const int* block_table, int table_stride, int n_tokens, int n_q_heads,
                   int n_kv_heads, int head_dim, float scale, int window, int n_splits,
                   int keys_per_split, float* part_acc, float* part_ml, float sink,
-                  const float* sinks, cudaStream_t stream) {
+                  const float* sinks, int keep_first, const void* gate, int gate_stride,
+                  cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim > kGenericMaxDim || n_kv_heads <= 0 ||
       n_q_heads % n_kv_heads || n_q_heads > 65535 || n_splits < 1 || n_splits > 65535 ||
@@ -193,12 +209,14 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
   dim3 grid(n_tokens, n_q_heads, n_splits);
   attention_generic_kernel<T><<<grid, kAttnThreads, 0, stream>>>(
       (T*)out, (const T*)q, q_row_stride, positions, token_slot, cache, n_q_heads, scale, window,
-      n_splits, keys_per_split, part_acc, part_ml, sink, sinks);
+      n_splits, keys_per_split, part_acc, part_ml, sink, sinks, window > 0 ? keep_first : 0,
+      (const T*)gate, gate_stride);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || n_splits == 1) return (int)e;
   dim3 cgrid(n_tokens, n_q_heads);
   attention_combine_kernel<T><<<cgrid, 64, 0, stream>>>((T*)out, part_acc, part_ml, n_q_heads,
-                                                        head_dim, n_splits, sink, sinks);
+                                                        head_dim, n_splits, sink, sinks,
+                                                        (const T*)gate, gate_stride);
   EK_RETURN_LAUNCH_STATUS();
 }
 
@@ -210,11 +228,12 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
       const void* k_pages, const void* v_pages, const int* block_table, int table_stride,      \
       int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, float scale, int window,      \
       int n_splits, int keys_per_split, float* part_acc, float* part_ml, float sink,           \
-      const float* sinks, cudaStream_t stream) {                                                                   \
+      const float* sinks, int keep_first, const void* gate, int gate_stride,                   \
+      cudaStream_t stream) {                                                                   \
     return ek::launch<T>(out, q, q_row_stride, positions, token_slot, k_pages, v_pages,        \
                          block_table, table_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, \
                          scale, window, n_splits, keys_per_split, part_acc, part_ml, sink,     \
-                         sinks, stream);                                                              \
+                         sinks, keep_first, gate, gate_stride, stream);                        \
   }
 
 EK_INSTANTIATE(f32, float)

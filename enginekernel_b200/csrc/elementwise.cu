@@ -148,11 +148,58 @@ rmsnorm_reg_kernel(T* __restrict__ y, float* resid, const T* add, const float* _
   }
 }
 
+// The same norm behind a sum of two sublayer outputs, each multiplied element by element by a 32-bit
+// vector of the stream's width first (a learned scale per channel): stream += a * sa + b * sb, then
+// y = gain * n(stream).  `b` (with `sb`) may be absent; `sa` / `sb` absent count as ones.  For layers
+// whose mixer and feed-forward read the same normed input and are added together.
+template <typename T>
+__global__ void rmsnorm_scaled_sum_kernel(T* __restrict__ y, float* resid, const T* __restrict__ a,
+                                          const float* __restrict__ sa, const T* __restrict__ b,
+                                          const float* __restrict__ sb, const float* __restrict__ gain,
+                                          const int* rows, float eps, int hidden, int write_back) {
+  __shared__ float scratch[33];
+  extern __shared__ __align__(16) float row_cache[];          // `hidden` floats
+  pdl_launch_dependents();
+  pdl_wait();
+  const int out_row = blockIdx.x;
+  const int src_row = rows ? rows[out_row] : out_row;
+  float* r = resid + (size_t)src_row * hidden;
+  const T* ar = a + (size_t)src_row * hidden;
+  const T* br = b ? b + (size_t)src_row * hidden : nullptr;
+  T* out = y + (size_t)out_row * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float add = to_f<T>(ar[i]) * (sa ? sa[i] : 1.f);
+    if (br) add = fmaf(to_f<T>(br[i]), sb ? sb[i] : 1.f, add);
+    const float v = r[i] + add;
+    if (write_back) r[i] = v;
+    row_cache[i] = v;
+    ss += v * v;
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    out[i] = from_f<T>(row_cache[i] * rstd * gain[i]);
+}
+
 // stream += add, without a norm (the last feed-forward output when no norm follows)
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ resid, const T* __restrict__ add, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) resid[i] += to_f<T>(add[i]);
+}
+
+// stream[r, i] += a[r, i] * sa[i] + b[r, i] * sb[i] without a norm (`b` may be absent; absent scales
+// count as ones): the last layer's outputs of a model whose layers scale them per channel
+template <typename T>
+__global__ void add_scaled_kernel(float* __restrict__ resid, const T* __restrict__ a, const float* __restrict__ sa,
+                                  const T* __restrict__ b, const float* __restrict__ sb, size_t n, int hidden) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int c = (int)(i % hidden);
+  float add = to_f<T>(a[i]) * (sa ? sa[c] : 1.f);
+  if (b) add = fmaf(to_f<T>(b[i]), sb ? sb[c] : 1.f, add);
+  resid[i] += add;
 }
 
 // out[r, i] = act(gu[r, i]) * gu[r, inter + i]    (silu: engine/ek_kernels.py:125-143)
@@ -283,11 +330,36 @@ using namespace ek;
                                     int write_back, cudaStream_t stream) {                      \
     return launch_rmsnorm<T>(y, resid, add, gain, rows, eps, n_rows, hidden, write_back, stream); \
   }                                                                                             \
+  EK_EXPORT int ek_rmsnorm_scaled_sum_##SUFFIX(void* y, float* resid, const void* a, const float* sa, \
+                                               const void* b, const float* sb, const float* gain, \
+                                               const int* rows, float eps, int n_rows, int hidden, \
+                                               int write_back, cudaStream_t stream) {           \
+    if (n_rows <= 0) return 0;                                                                  \
+    if (hidden <= 0 || (size_t)hidden * 4 > 200 * 1024 || a == nullptr) return EK_ERR_ARG;      \
+    const size_t smem = (size_t)hidden * sizeof(float);                                         \
+    auto kernel = ek::rmsnorm_scaled_sum_kernel<T>;                                             \
+    if (smem > 40 * 1024) {                                                                     \
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                      \
+    }                                                                                           \
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);                     \
+    return (int)ek::launch_pdl(kernel, dim3(n_rows), dim3(threads), smem, stream, (T*)y, resid, \
+                               (const T*)a, sa, (const T*)b, sb, gain, rows, eps, hidden,       \
+                               write_back);                                                     \
+  }                                                                                             \
   EK_EXPORT int ek_add_residual_##SUFFIX(float* resid, const void* add, long long n,            \
                                          cudaStream_t stream) {                                 \
     if (n <= 0) return 0;                                                                       \
     add_residual_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(resid, (const T*)add, \
                                                                              (size_t)n);        \
+    EK_RETURN_LAUNCH_STATUS();                                                                  \
+  }                                                                                             \
+  EK_EXPORT int ek_add_scaled_##SUFFIX(float* resid, const void* a, const float* sa, const void* b, \
+                                       const float* sb, long long n, int hidden, cudaStream_t stream) { \
+    if (n <= 0) return 0;                                                                       \
+    if (hidden <= 0 || a == nullptr) return EK_ERR_ARG;                                         \
+    add_scaled_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(                      \
+        resid, (const T*)a, sa, (const T*)b, sb, (size_t)n, hidden);                            \
     EK_RETURN_LAUNCH_STATUS();                                                                  \
   }                                                                                             \
   EK_EXPORT int ek_silu_mul_##SUFFIX(void* out, const void* gu, int rows, int inter,            \

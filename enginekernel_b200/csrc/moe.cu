@@ -4,7 +4,9 @@
 //   route     scores = softmax(logits) over all experts (32-bit); experts form `n_groups` equal
 //             groups of neighbours, a group's score is its best expert's, only experts of the
 //             `keep` best groups can be chosen; the `top` largest of those; weights = chosen
-//             scores / (their sum + 1e-20) * scale.  A warp a token.
+//             scores / (their sum + 1e-20) * scale.  A warp a token.  `among_chosen`: the weights are
+//             the softmax over the chosen logits alone (times scale), taken from the logits with the
+//             chosen maximum off, so that no score can vanish against an unchosen expert's.
 //   plan      the (token, choice) pairs sorted by expert, and the row tiles of every expert's
 //             stretch, made on the device: the host never sees who chose what.
 //   expert product  out[row] = f(x[row] . W_e^T) over the tiles of the plan: FFMA with 32-bit
@@ -12,7 +14,9 @@
 //             at a time), or mma.sync on bfloat16 tiles with 32-bit accumulators; either way a
 //             pair's result does not depend on its neighbours.  The up form gathers its rows by
 //             token and applies the activation, the down form scales by the pair's weight and
-//             scatters 32-bit rows by pair.
+//             scatters 32-bit rows by pair.  `gated` up form: the expert's weight rows alternate
+//             gate, up, gate, up ...; column pair (2c, 2c + 1) of the product gives out[c] =
+//             act(gate) * up from the 32-bit sums (N counts the weight rows, the output has N / 2).
 //   combine   out[t] = sum over the token's choices, in the order they were chosen.
 #include "common.cuh"
 
@@ -33,7 +37,7 @@ constexpr int kRouteWarps = 4;
 __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_kernel(int* __restrict__ sel_expert, float* __restrict__ sel_weight,
                  const float* __restrict__ logits, int n_tokens, int E, int n_groups, int keep, int top,
-                 float scale) {
+                 float scale, int among_chosen) {
   extern __shared__ float route_s[];            // per warp: scores [E], candidates [E], groups [n_groups]
   pdl_launch_dependents();
   pdl_wait();
@@ -51,7 +55,10 @@ moe_route_kernel(int* __restrict__ sel_expert, float* __restrict__ sel_weight,
   for (int e = lane; e < E; e += 32) { const float x = expf(z[e] - m); s[e] = x; sum += x; }
   sum = warp_sum(sum);
   const float inv = 1.f / sum;
-  for (int e = lane; e < E; e += 32) { s[e] *= inv; cand[e] = s[e]; }
+  // candidates: the scores; with weights among the chosen the logits themselves, so that the order of
+  // two experts whose scores both round to nothing is still the order of their logits
+  const float shut = among_chosen ? -INFINITY : -2.f;
+  for (int e = lane; e < E; e += 32) { s[e] *= inv; cand[e] = among_chosen ? z[e] : s[e]; }
   __syncwarp();
   if (n_groups > 1 && keep < n_groups) {
     const int per = E / n_groups;
@@ -70,23 +77,33 @@ moe_route_kernel(int* __restrict__ sel_expert, float* __restrict__ sel_weight,
       __syncwarp();
     }
     for (int e = lane; e < E; e += 32)
-      if (gs[e / per] != -3.f) cand[e] = -1.f;
+      if (gs[e / per] != -3.f) cand[e] = among_chosen ? -INFINITY : -1.f;
     __syncwarp();
   }
   float total = 0.f;
   for (int k = 0; k < top; ++k) {
-    float bv = -2.f; int bi = 0x7fffffff;
+    float bv = shut; int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32)
       if (cand[e] > bv) { bv = cand[e]; bi = e; }
     warp_argmax(bv, bi);
+    if (bi >= E) bi = 0;                        // (no finite candidate left: logits that are not numbers)
     const float sc = s[bi];
     total += sc;
     if (lane == 0) {
       sel_expert[(size_t)t * top + k] = bi;
       sel_weight[(size_t)t * top + k] = sc;     // scaled below
-      cand[bi] = -2.f;
+      cand[bi] = shut;
     }
     __syncwarp();
+  }
+  if (among_chosen) {                           // softmax over the chosen logits: the first chosen is the largest
+    __syncwarp();
+    const float z0 = z[sel_expert[(size_t)t * top]];
+    float den = 0.f;
+    for (int k = 0; k < top; ++k) den += expf(z[sel_expert[(size_t)t * top + k]] - z0);
+    for (int k = lane; k < top; k += 32)
+      sel_weight[(size_t)t * top + k] = expf(z[sel_expert[(size_t)t * top + k]] - z0) / den * scale;
+    return;
   }
   const float f = scale / (total + 1e-20f);
   for (int k = lane; k < top; k += 32) sel_weight[(size_t)t * top + k] *= f;
@@ -156,7 +173,7 @@ __global__ void __launch_bounds__(256)
 moe_expert_product_kernel(void* __restrict__ out_, const T* __restrict__ a, const T* __restrict__ w,
                           const int* __restrict__ tiles, const int* __restrict__ n_tiles,
                           const int* __restrict__ sorted_pair, const float* __restrict__ pair_weight,
-                          int top, int N, int K, int act) {
+                          int top, int N, int K, int act, int gated) {
   constexpr int BM = kTileRows, BN = 64, BK = 16, TM = 4, TN = 4, PAD = 4;
   __shared__ __align__(16) float As[BK][BM + PAD];
   __shared__ __align__(16) float Ws[BK][BN + PAD];
@@ -215,7 +232,10 @@ moe_expert_product_kernel(void* __restrict__ out_, const T* __restrict__ a, cons
     for (int j = 0; j < TN; ++j) {
       const int gn = n0 + tx * TN + j;
       if (gn >= N) continue;
-      if (UP) {
+      if (UP && gated) {                          // columns (gn, gn + 1) = (gate, up); N is even
+        if (!(j & 1)) ((T*)out_)[(size_t)(row0 + r) * (N / 2) + gn / 2] =
+            from_f<T>(activate(acc[i][j], act) * acc[i][j + 1]);
+      } else if (UP) {
         ((T*)out_)[(size_t)(row0 + r) * N + gn] = from_f<T>(activate(acc[i][j], act));
       } else {
         const int p = pair_s[r];
@@ -262,7 +282,7 @@ __global__ void __launch_bounds__(256)
 moe_expert_product_tc_kernel(void* __restrict__ out_, const bf16* __restrict__ a, const bf16* __restrict__ w,
                              const int* __restrict__ tiles, const int* __restrict__ n_tiles,
                              const int* __restrict__ sorted_pair, const float* __restrict__ pair_weight,
-                             int top, int N, int K, int act) {
+                             int top, int N, int K, int act, int gated) {
   constexpr int BM = kTileRows, BN = kTcCols, BK = kTcK, LD = kTcLd, STAGES = kTcStages;
   extern __shared__ __align__(16) unsigned char tc_smem[];
   typedef bf16 (*Tile)[LD];
@@ -350,6 +370,16 @@ moe_expert_product_tc_kernel(void* __restrict__ out_, const bf16* __restrict__ a
       if (r >= rows) continue;
       const int p = pair_s[r];
       const float pw = UP ? 1.f : pair_weight[p];
+      if (UP && gated) {                          // a lane's two neighbouring columns are (gate, up)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int gn = n0 + wn * 32 + j * 8 + tq * 2;
+          if (gn + 1 < N)
+            ((bf16*)out_)[(size_t)(row0 + r) * (N / 2) + gn / 2] =
+                __float2bfloat16_rn(activate(acc[i][j][half * 2], act) * acc[i][j][half * 2 + 1]);
+        }
+        continue;
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -382,7 +412,8 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict_
 EK_EXPORT int ek_moe_tile_rows() { return ek::kTileRows; }
 
 EK_EXPORT int ek_moe_route(int* sel_expert, float* sel_weight, const float* logits, int n_tokens, int E,
-                           int n_groups, int keep, int top, float scale, cudaStream_t stream) {
+                           int n_groups, int keep, int top, float scale, int among_chosen,
+                           cudaStream_t stream) {
   using namespace ek;
   if (n_tokens <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups ||
@@ -395,7 +426,7 @@ EK_EXPORT int ek_moe_route(int* sel_expert, float* sel_weight, const float* logi
     if (e != cudaSuccess) return (int)e;
   }
   moe_route_kernel<<<(n_tokens + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, stream>>>(
-      sel_expert, sel_weight, logits, n_tokens, E, n_groups, keep, top, scale);
+      sel_expert, sel_weight, logits, n_tokens, E, n_groups, keep, top, scale, among_chosen);
   EK_RETURN_LAUNCH_STATUS();
 }
 
@@ -411,9 +442,10 @@ EK_EXPORT int ek_moe_plan(int* sorted_pair, int* tiles, int* n_tiles, const int*
 // The tensor-core forms: bfloat16, K a multiple of 8, operands on 16-byte boundaries.
 EK_EXPORT int ek_moe_expert_up_tc(void* out, const void* x, const void* w, const int* tiles, const int* n_tiles,
                                   const int* sorted_pair, int max_tiles, int top, int N, int K, int act,
-                                  cudaStream_t stream) {
+                                  int gated, cudaStream_t stream) {
   using namespace ek;
   if (max_tiles <= 0) return 0;
+  if (gated && N % 2) return EK_ERR_ARG;
   if (N <= 0 || K <= 0 || K % 8 || top <= 0 || (N + 127) / 128 > 65535 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return EK_ERR_ARG;
   dim3 grid(max_tiles, (N + 127) / 128);
@@ -421,7 +453,7 @@ EK_EXPORT int ek_moe_expert_up_tc(void* out, const void* x, const void* w, const
                                        (int)kTcSmem);
   if (e != cudaSuccess) return (int)e;
   moe_expert_product_tc_kernel<true><<<grid, 256, kTcSmem, stream>>>(out, (const bf16*)x, (const bf16*)w, tiles, n_tiles,
-                                                              sorted_pair, nullptr, top, N, K, act);
+                                                              sorted_pair, nullptr, top, N, K, act, gated);
   EK_RETURN_LAUNCH_STATUS();
 }
 
@@ -437,20 +469,21 @@ EK_EXPORT int ek_moe_expert_down_tc(float* out, const void* a, const void* w, co
                                        (int)kTcSmem);
   if (e != cudaSuccess) return (int)e;
   moe_expert_product_tc_kernel<false><<<grid, 256, kTcSmem, stream>>>(out, (const bf16*)a, (const bf16*)w, tiles, n_tiles,
-                                                               sorted_pair, pair_weight, 1, N, K, 0);
+                                                               sorted_pair, pair_weight, 1, N, K, 0, 0);
   EK_RETURN_LAUNCH_STATUS();
 }
 
 #define EK_INSTANTIATE(SUFFIX, T)                                                                     \
   EK_EXPORT int ek_moe_expert_up_##SUFFIX(void* out, const void* x, const void* w, const int* tiles,  \
                                           const int* n_tiles, const int* sorted_pair, int max_tiles,  \
-                                          int top, int N, int K, int act, cudaStream_t stream) {      \
+                                          int top, int N, int K, int act, int gated,                  \
+                                          cudaStream_t stream) {                                      \
     using namespace ek;                                                                               \
     if (max_tiles <= 0) return 0;                                                                     \
-    if (N <= 0 || K <= 0 || top <= 0 || (N + 63) / 64 > 65535) return EK_ERR_ARG;                     \
+    if (N <= 0 || K <= 0 || top <= 0 || (N + 63) / 64 > 65535 || (gated && N % 2)) return EK_ERR_ARG; \
     dim3 grid(max_tiles, (N + 63) / 64);                                                              \
     moe_expert_product_kernel<T, true><<<grid, 256, 0, stream>>>(                                     \
-        out, (const T*)x, (const T*)w, tiles, n_tiles, sorted_pair, nullptr, top, N, K, act);         \
+        out, (const T*)x, (const T*)w, tiles, n_tiles, sorted_pair, nullptr, top, N, K, act, gated);  \
     EK_RETURN_LAUNCH_STATUS();                                                                        \
   }                                                                                                   \
   EK_EXPORT int ek_moe_expert_down_##SUFFIX(float* out, const void* a, const void* w, const int* tiles, \
@@ -462,7 +495,7 @@ EK_EXPORT int ek_moe_expert_down_tc(float* out, const void* a, const void* w, co
     if (N <= 0 || K <= 0 || (N + 63) / 64 > 65535) return EK_ERR_ARG;                                 \
     dim3 grid(max_tiles, (N + 63) / 64);                                                              \
     moe_expert_product_kernel<T, false><<<grid, 256, 0, stream>>>(                                    \
-        out, (const T*)a, (const T*)w, tiles, n_tiles, sorted_pair, pair_weight, 1, N, K, 0);         \
+        out, (const T*)a, (const T*)w, tiles, n_tiles, sorted_pair, pair_weight, 1, N, K, 0, 0);      \
     EK_RETURN_LAUNCH_STATUS();                                                                        \
   }                                                                                                   \
   EK_EXPORT int ek_moe_combine_##SUFFIX(void* out, const float* pair_out, int n_tokens, int top,      \

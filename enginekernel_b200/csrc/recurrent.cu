@@ -1,0 +1,379 @@
+// Linear recurrences with one decay per head and token, as mixers with per-sequence state:
+//     S_t = a_t S_(t-1) + b_t k_t v_t^T        o_t = S_t^T q_t        (S is [dk, dv] per head, 32-bit)
+// Two designs of mixer reduce to it.  A state-space layer (state-space duality): k = B_t, q = C_t of
+// the head's group, v = x_t, a = exp(-exp(A_log) dt), b = dt, dt = softplus(raw + bias).  A matrix
+// memory with exponential gates (mLSTM): a = exp(f + m_(t-1) - m_t), b = exp(i - m_t) with the
+// running maximum m_t = max(f + m_(t-1), i) and capped gate pre-activations; its normaliser
+// n_t = a n + b k is one more column of S whose v is 1.
+//
+// A column of S never meets another, so the scan runs one column per group of 8 lanes, the column's
+// rows in the lanes' registers, sequentially over a sequence's tokens and in parallel over sequences,
+// heads and columns.  All kernels take packed rows of several sequences (prompts, portions, single
+// tokens); rows whose position is negative belong to finished sequences and are skipped.
+//
+//   conv_silu        causal convolution per channel with bias, then SiLU; predecessors are found in the
+//                    step by slot and position, or in the state's tail
+//   conv_tail        the last taps-1 convolution inputs of every sequence -> its state
+//   ssm_gates        a, b of the state-space layer
+//   xgate_scan       a, b and the running maximum of the matrix memory (a warp a head, 32 tokens a pass)
+//   decay_scan       the recurrence; reads and writes S in the state
+//   ssm_out          (o + D x) silu(z), RMS norm in equal parts, weight -> activation type
+//   xlstm_out        o / (max(|n.q|, exp(-m)) + 1e-6), RMS norm per head, weight, sigmoid gate
+// Everything here is 32-bit; only the two output kernels round, once, to the activation type.
+#include "common.cuh"
+
+namespace ek {
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+// ln(1 + e^x); beyond 20 the sum rounds to e^x in 32 bits, so x itself is the exact result
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// Predecessors of token t inside the step (same slot, positions counting down), at most `most`.
+__device__ __forceinline__ int step_predecessors(const int* positions, const int* token_slot, int t, int most) {
+  const int slot = token_slot[t], pos = positions[t];
+  int n = 0;
+  while (n < most && t - n - 1 >= 0 && token_slot[t - n - 1] == slot && positions[t - n - 1] == pos - n - 1) ++n;
+  return n;
+}
+
+// grid: tokens.  out[t, c] = silu(bias[c] + sum_j w[c][K-1-j] x[t-j, c]) with x = proj[., col0 + c].
+// tail of a slot: [channels][K-1], oldest first.
+__global__ void __launch_bounds__(256)
+conv_silu_kernel(float* __restrict__ out, int out_stride, const float* __restrict__ proj, int proj_stride, int col0,
+                 const float* __restrict__ conv_w, const float* __restrict__ conv_b,
+                 const float* __restrict__ state, size_t slot_stride, size_t tail_offset,
+                 const int* __restrict__ positions, const int* __restrict__ token_slot, int channels, int K) {
+  __shared__ int n_prev_s;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (positions[t] < 0) return;
+  if (threadIdx.x == 0) n_prev_s = step_predecessors(positions, token_slot, t, K - 1);
+  __syncthreads();
+  const int n_prev = n_prev_s;
+  const float* tail = state + (size_t)token_slot[t] * slot_stride + tail_offset;
+  const float* row = proj + (size_t)t * proj_stride + col0;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    const float* w = conv_w + (size_t)c * K;
+    float acc = (conv_b ? conv_b[c] : 0.f) + w[K - 1] * row[c];
+    for (int j = 1; j < K; ++j) {
+      const float x = j <= n_prev ? proj[(size_t)(t - j) * proj_stride + col0 + c]
+                                  : tail[(size_t)c * (K - 1) + (n_prev - j + K - 1)];
+      acc = fmaf(w[K - 1 - j], x, acc);
+    }
+    out[(size_t)t * out_stride + c] = acc * sigmoid_f(acc);
+  }
+}
+
+// grid (sequences, channel tiles).  After the step the tail holds the sequence's last taps-1 inputs.
+__global__ void conv_tail_kernel(float* __restrict__ state, size_t slot_stride, size_t tail_offset,
+                                 const float* __restrict__ proj, int proj_stride, int col0,
+                                 const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
+                                 const int* __restrict__ token_slot, int channels, int taps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+  if (n <= 0 || positions[start] < 0) return;
+  float* tail = state + (size_t)token_slot[start] * slot_stride + tail_offset;
+  const int keep = taps - 1;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
+    float* tc = tail + (size_t)c * keep;
+    for (int m = 0; m < keep; ++m) {
+      const int from_step = n - keep + m;       // row of the step that lands at place m
+      tc[m] = from_step >= 0 ? proj[(size_t)(start + from_step) * proj_stride + col0 + c] : tc[m + n];
+    }
+  }
+}
+
+// a[t, h] = exp(-exp(a_log[h]) dt), b[t, h] = dt, dt = softplus(proj[t, col0 + h] + dt_bias[h]).
+__global__ void ssm_gates_kernel(float* __restrict__ a, float* __restrict__ b, const float* __restrict__ proj,
+                                 int proj_stride, int col0, const float* __restrict__ dt_bias,
+                                 const float* __restrict__ a_log, int n_tokens, int heads) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_tokens * heads) return;
+  const int t = idx / heads, h = idx % heads;
+  const float dt = softplus_f(proj[(size_t)t * proj_stride + col0 + h] + dt_bias[h]);
+  a[idx] = expf(-expf(a_log[h]) * dt);
+  b[idx] = dt;
+}
+
+// grid (sequences, heads / warps a block); a warp a head.  Log input gate i = cap tanh((x_i + b_i) / cap),
+// log forget gate f = logsigmoid(cap tanh((x_f + b_f) / cap)); m_t = max(f_t + m_(t-1), i_t) from the
+// state's m; a = exp(f + m_(t-1) - m_t), b = exp(i - m_t), m_run[t, h] = m_t.  The maximum over 32 tokens
+// at a time: the maps m -> max(m + F, I) compose as (F1 + F2, max(I1 + F2, I2)).
+constexpr int kGateWarps = 4;
+__global__ void __launch_bounds__(kGateWarps * 32)
+xgate_scan_kernel(float* __restrict__ a, float* __restrict__ b, float* __restrict__ m_run,
+                  const float* __restrict__ proj, int proj_stride, int col_i, int col_f,
+                  const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap,
+                  float* __restrict__ state, size_t slot_stride, size_t m_offset,
+                  const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
+                  const int* __restrict__ token_slot, int heads, int write_state) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.x, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * kGateWarps + (threadIdx.x >> 5);
+  if (h >= heads) return;
+  const int start = cu_seqlens[seq], n = cu_seqlens[seq + 1] - start;
+  if (n <= 0 || positions[start] < 0) return;
+  float* m_state = state + (size_t)token_slot[start] * slot_stride + m_offset + h;
+  float m_in = *m_state;
+  const float bi = bias_i[h], bf = bias_f[h];
+  for (int c0 = 0; c0 < n; c0 += 32) {
+    const int t = start + c0 + lane;
+    const bool live = c0 + lane < n;
+    float gi = 0.f, gf = 0.f;                    // the identity map for lanes past the end: F = 0, I = -inf
+    if (live) {
+      const float* row = proj + (size_t)t * proj_stride;
+      gi = cap * tanhf((row[col_i + h] + bi) / cap);
+      gf = -softplus_f(-(cap * tanhf((row[col_f + h] + bf) / cap)));
+    }
+    float F = live ? gf : 0.f, I = live ? gi : -INFINITY;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {           // inclusive scan: the maps of tokens c0 .. c0 + lane composed
+      const float F1 = __shfl_up_sync(0xffffffffu, F, o), I1 = __shfl_up_sync(0xffffffffu, I, o);
+      if (lane >= o) { I = fmaxf(I1 + F, I); F = F1 + F; }
+    }
+    const float m = fmaxf(m_in + F, I);
+    float m_prev = __shfl_up_sync(0xffffffffu, m, 1);
+    if (lane == 0) m_prev = m_in;
+    if (live) {
+      a[(size_t)t * heads + h] = expf(gf + m_prev - m);
+      b[(size_t)t * heads + h] = expf(gi - m);
+      m_run[(size_t)t * heads + h] = m;
+    }
+    m_in = __shfl_sync(0xffffffffu, m, 31);      // lanes past the end carry the last live value on
+  }
+  if (write_state && lane == 0) *m_state = m_in;
+}
+
+constexpr int kScanCols = 16;        // columns of S a block takes
+constexpr int kScanLanes = 8;        // lanes that share a column
+constexpr int kScanChunk = 16;       // tokens fetched into shared memory at a time
+constexpr int kScanThreads = kScanCols * kScanLanes;
+
+// grid (sequences, heads, column tiles).  RPL rows of a column a lane: lane l holds rows 32 g + 4 l + c
+// (g < RPL / 4, c < 4), so that the 8 lanes of a column read 128 neighbouring bytes of a key at a time.
+// S of a slot: state[((h * C + j) * DK + i], DK = 8 RPL rows (keys padded with zeros), C = dv + ones_col columns.
+// Column dv (with ones_col) has v = 1: it carries n_t = a n + b k and gives n.q.
+template <int RPL>
+__global__ void __launch_bounds__(kScanThreads)
+decay_scan_kernel(float* __restrict__ out, int out_stride, const float* __restrict__ q, int q_stride,
+                  const float* __restrict__ k, int k_stride, const float* __restrict__ v, int v_stride,
+                  const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ state,
+                  size_t slot_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
+                  const int* __restrict__ token_slot, int heads, int kv_heads, int dk, int dv, int ones_col,
+                  int write_state) {
+  constexpr int DK = 8 * RPL, G4 = RPL / 4;
+  __shared__ __align__(16) float k_s[kScanChunk][DK];
+  __shared__ __align__(16) float q_s[kScanChunk][DK];
+  __shared__ float v_s[kScanChunk][kScanCols];
+  __shared__ float a_s[kScanChunk], b_s[kScanChunk];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kScanCols;
+  const int start = cu_seqlens[seq], n = cu_seqlens[seq + 1] - start;
+  if (n <= 0 || positions[start] < 0) return;
+  const int tid = threadIdx.x, col = tid / kScanLanes, lane = tid % kScanLanes;
+  const int C = dv + ones_col, j = col0 + col;
+  const bool live = j < C;
+  const int kv = h / (heads / kv_heads);
+  float* sp = state + (size_t)token_slot[start] * slot_stride + ((size_t)h * C + (live ? j : 0)) * DK;
+  float4 S[G4];
+#pragma unroll
+  for (int g = 0; g < G4; ++g)
+    S[g] = live ? *reinterpret_cast<const float4*>(sp + 32 * g + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = 0; c0 < n; c0 += kScanChunk) {
+    const int nc = min(kScanChunk, n - c0);
+    __syncthreads();                             // the chunk before is worked through
+    for (int idx = tid; idx < nc * DK; idx += kScanThreads) {
+      const int tt = idx / DK, i = idx % DK;
+      const size_t t = start + c0 + tt;
+      k_s[tt][i] = i < dk ? k[t * k_stride + (size_t)kv * dk + i] : 0.f;
+      q_s[tt][i] = i < dk ? q[t * q_stride + (size_t)kv * dk + i] : 0.f;
+    }
+    for (int idx = tid; idx < nc * kScanCols; idx += kScanThreads) {
+      const int tt = idx / kScanCols, cc = idx % kScanCols, jj = col0 + cc;
+      const size_t t = start + c0 + tt;
+      v_s[tt][cc] = jj < dv ? v[t * v_stride + (size_t)h * dv + jj] : (jj < C ? 1.f : 0.f);
+    }
+    if (tid < nc) {
+      a_s[tid] = a[(size_t)(start + c0 + tid) * heads + h];
+      b_s[tid] = b[(size_t)(start + c0 + tid) * heads + h];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nc; ++tt) {
+      const float aa = a_s[tt], bv = b_s[tt] * v_s[tt][col];
+      float acc = 0.f;
+#pragma unroll
+      for (int g = 0; g < G4; ++g) {
+        const float4 kk = *reinterpret_cast<const float4*>(&k_s[tt][32 * g + 4 * lane]);
+        const float4 qq = *reinterpret_cast<const float4*>(&q_s[tt][32 * g + 4 * lane]);
+        S[g].x = fmaf(aa, S[g].x, bv * kk.x);
+        S[g].y = fmaf(aa, S[g].y, bv * kk.y);
+        S[g].z = fmaf(aa, S[g].z, bv * kk.z);
+        S[g].w = fmaf(aa, S[g].w, bv * kk.w);
+        acc = fmaf(S[g].x, qq.x, acc);
+        acc = fmaf(S[g].y, qq.y, acc);
+        acc = fmaf(S[g].z, qq.z, acc);
+        acc = fmaf(S[g].w, qq.w, acc);
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      if (lane == 0 && live) out[(size_t)(start + c0 + tt) * out_stride + (size_t)h * C + j] = acc;
+    }
+  }
+  if (write_state && live) {
+#pragma unroll
+    for (int g = 0; g < G4; ++g) *reinterpret_cast<float4*>(sp + 32 * g + 4 * lane) = S[g];
+  }
+}
+
+// grid (tokens, parts).  y[t, c] = rms-normed over the part ((o + D[h] x) silu(z)) * w[c]; o [T, inner] from
+// the scan, x [T, .] the convolved inputs (stride x_stride), z = proj[t, col_z + c]; a head is vdim channels.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ssm_out_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __restrict__ x, int x_stride,
+               const float* __restrict__ proj, int proj_stride, int col_z, const float* __restrict__ d_skip,
+               const float* __restrict__ w, float eps, const int* __restrict__ positions, int inner, int vdim,
+               int parts) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, part = blockIdx.y;
+  if (positions[t] < 0) return;
+  const int size = inner / parts, c0 = part * size;
+  auto value = [&](int c) {
+    const float z = proj[(size_t)t * proj_stride + col_z + c];
+    return (o[(size_t)t * inner + c] + d_skip[c / vdim] * x[(size_t)t * x_stride + c]) * (z * sigmoid_f(z));
+  };
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < size; i += blockDim.x) { const float u = value(c0 + i); ss += u * u; }
+  const float rstd = rsqrtf(block_sum(ss, scratch) / (float)size + eps);
+  for (int i = threadIdx.x; i < size; i += blockDim.x)
+    y[(size_t)t * inner + c0 + i] = from_f<T>(value(c0 + i) * rstd * w[c0 + i]);
+}
+
+// grid (tokens, heads).  o [T, heads * (vdim + 1)] from the scan with n.q in each head's last column, both
+// still to be multiplied by q_scale; y[t, h, j] = u / rms(u) * w[h vdim + j] * sigmoid(gate), u = o q_scale /
+// (max(|n.q| q_scale, exp(-m)) + 1e-6), gate = proj[t, col_g + h vdim + j].
+template <typename T>
+__global__ void __launch_bounds__(128)
+xlstm_out_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __restrict__ m_run,
+                 const float* __restrict__ proj, int proj_stride, int col_g, const float* __restrict__ w,
+                 float eps, float q_scale, const int* __restrict__ positions, int heads, int vdim) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  if (positions[t] < 0) return;
+  const float* oh = o + ((size_t)t * heads + h) * (vdim + 1);
+  const float den = fmaxf(fabsf(oh[vdim] * q_scale), expf(-m_run[(size_t)t * heads + h])) + 1e-6f;
+  const float f = q_scale / den;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < vdim; i += blockDim.x) { const float u = oh[i] * f; ss += u * u; }
+  const float rstd = rsqrtf(block_sum(ss, scratch) / (float)vdim + eps);
+  for (int i = threadIdx.x; i < vdim; i += blockDim.x) {
+    const int c = h * vdim + i;
+    y[((size_t)t * heads) * vdim + c] =
+        from_f<T>(oh[i] * f * rstd * w[c] * sigmoid_f(proj[(size_t)t * proj_stride + col_g + c]));
+  }
+}
+
+}  // namespace ek
+
+EK_EXPORT int ek_conv_silu(float* out, int out_stride, const float* proj, int proj_stride, int col0,
+                           const float* conv_w, const float* conv_b, const float* state, long long slot_stride,
+                           long long tail_offset, const int* positions, const int* token_slot, int n_tokens,
+                           int channels, int taps, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (channels <= 0 || taps < 1) return EK_ERR_ARG;
+  return (int)ek::launch_pdl(ek::conv_silu_kernel, dim3(n_tokens), dim3(256), 0, stream, out, out_stride, proj,
+                             proj_stride, col0, conv_w, conv_b, state, (size_t)slot_stride, (size_t)tail_offset,
+                             positions, token_slot, channels, taps);
+}
+
+EK_EXPORT int ek_conv_tail(float* state, long long slot_stride, long long tail_offset, const float* proj,
+                           int proj_stride, int col0, const int* cu_seqlens, const int* positions,
+                           const int* token_slot, int n_seqs, int channels, int taps, cudaStream_t stream) {
+  if (n_seqs <= 0 || taps <= 1) return 0;
+  const int tiles = (channels + 255) / 256;
+  return (int)ek::launch_pdl(ek::conv_tail_kernel, dim3(n_seqs, tiles < 64 ? tiles : 64), dim3(256), 0, stream, state,
+                             (size_t)slot_stride, (size_t)tail_offset, proj, proj_stride, col0, cu_seqlens,
+                             positions, token_slot, channels, taps);
+}
+
+EK_EXPORT int ek_ssm_gates(float* a, float* b, const float* proj, int proj_stride, int col0, const float* dt_bias,
+                           const float* a_log, int n_tokens, int heads, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (heads <= 0) return EK_ERR_ARG;
+  const long long total = (long long)n_tokens * heads;
+  return (int)ek::launch_pdl(ek::ssm_gates_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, a, b,
+                             proj, proj_stride, col0, dt_bias, a_log, n_tokens, heads);
+}
+
+EK_EXPORT int ek_xgate_scan(float* a, float* b, float* m_run, const float* proj, int proj_stride, int col_i,
+                            int col_f, const float* bias_i, const float* bias_f, float cap, float* state,
+                            long long slot_stride, long long m_offset, const int* cu_seqlens, const int* positions,
+                            const int* token_slot, int n_seqs, int heads, int write_state, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (heads <= 0 || !(cap > 0.f)) return EK_ERR_ARG;
+  return (int)ek::launch_pdl(ek::xgate_scan_kernel, dim3(n_seqs, (heads + ek::kGateWarps - 1) / ek::kGateWarps),
+                             dim3(ek::kGateWarps * 32), 0, stream, a, b, m_run, proj, proj_stride, col_i, col_f,
+                             bias_i, bias_f, cap, state, (size_t)slot_stride, (size_t)m_offset, cu_seqlens,
+                             positions, token_slot, heads, write_state);
+}
+
+// Rows of S per column that the scan keeps for keys of dk values: dk rounded up to 32, 64, 128 or 256.
+EK_EXPORT int ek_decay_scan_rows(int dk) {
+  return dk <= 0 || dk > 256 ? 0 : dk <= 32 ? 32 : dk <= 64 ? 64 : dk <= 128 ? 128 : 256;
+}
+
+EK_EXPORT int ek_decay_scan(float* out, int out_stride, const float* q, int q_stride, const float* k, int k_stride,
+                            const float* v, int v_stride, const float* a, const float* b, float* state,
+                            long long slot_stride, const int* cu_seqlens, const int* positions,
+                            const int* token_slot, int n_seqs, int heads, int kv_heads, int dk, int dv,
+                            int ones_col, int write_state, cudaStream_t stream) {
+  using namespace ek;
+  if (n_seqs <= 0) return 0;
+  const int rows = ek_decay_scan_rows(dk);
+  if (!rows || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dv <= 0 || heads > 65535 || slot_stride % 4 ||
+      ((uintptr_t)state & 15))
+    return EK_ERR_ARG;
+  const int C = dv + (ones_col ? 1 : 0);
+  dim3 grid(n_seqs, heads, (C + kScanCols - 1) / kScanCols);
+  auto kernel = rows == 32 ? decay_scan_kernel<4> : rows == 64 ? decay_scan_kernel<8>
+              : rows == 128 ? decay_scan_kernel<16> : decay_scan_kernel<32>;
+  return (int)launch_pdl(kernel, grid, dim3(kScanThreads), 0, stream, out, out_stride, q, q_stride, k, k_stride, v,
+                         v_stride, a, b, state, (size_t)slot_stride, cu_seqlens, positions, token_slot, heads,
+                         kv_heads, dk, dv, ones_col ? 1 : 0, write_state);
+}
+
+#define EK_INSTANTIATE(SUFFIX, T)                                                                              \
+  EK_EXPORT int ek_ssm_out_##SUFFIX(void* y, const float* o, const float* x, int x_stride, const float* proj,  \
+                                    int proj_stride, int col_z, const float* d_skip, const float* w, float eps, \
+                                    const int* positions, int n_tokens, int inner, int vdim, int parts,        \
+                                    cudaStream_t stream) {                                                     \
+    if (n_tokens <= 0) return 0;                                                                               \
+    if (inner <= 0 || vdim <= 0 || parts <= 0 || inner % parts || inner % vdim || parts > 65535)               \
+      return EK_ERR_ARG;                                                                                       \
+    return (int)ek::launch_pdl(ek::ssm_out_kernel<T>, dim3(n_tokens, parts), dim3(256), 0, stream, (T*)y, o, x, \
+                               x_stride, proj, proj_stride, col_z, d_skip, w, eps, positions, inner, vdim,     \
+                               parts);                                                                         \
+  }                                                                                                            \
+  EK_EXPORT int ek_xlstm_out_##SUFFIX(void* y, const float* o, const float* m_run, const float* proj,          \
+                                      int proj_stride, int col_g, const float* w, float eps, float q_scale,    \
+                                      const int* positions, int n_tokens, int heads, int vdim,                 \
+                                      cudaStream_t stream) {                                                   \
+    if (n_tokens <= 0) return 0;                                                                               \
+    if (heads <= 0 || heads > 65535 || vdim <= 0) return EK_ERR_ARG;                                           \
+    return (int)ek::launch_pdl(ek::xlstm_out_kernel<T>, dim3(n_tokens, heads), dim3(128), 0, stream, (T*)y, o, \
+                               m_run, proj, proj_stride, col_g, w, eps, q_scale, positions, heads, vdim);      \
+  }
+
+EK_INSTANTIATE(f32, float)
+EK_INSTANTIATE(bf16, ek::bf16)

@@ -134,6 +134,68 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
 }
 
 
+// Rotation first, then the head divided by its root mean square - for designs that turn queries and
+// keys before they normalise them, without a gain.  A warp a head.  The row of a token holds its query
+// heads from column 0, its key heads from `k_col` and its value heads from `v_col` (each `d` = the
+// cache's head size apart; key and value heads only when `write_kv`).  A head may be padded with zeros
+// beyond the values it really has: `norm_dim` is the count the mean is taken over.  `unit` 0: no norm.
+template <typename T>
+__global__ void qk_rope_unit_kv_kernel(T* rows, int row_stride, int k_col, int v_col,
+                                       const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                                       int rot_dim, const int* positions, const int* token_slot,
+                                       PagedKV cache, int n_q_heads, int norm_dim, float eps, int unit,
+                                       int write_kv) {
+  __shared__ float buf[kRopeWarps][EK_MAX_HEAD_DIM];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * kRopeWarps + warp;
+  const int n_kv = cache.heads, d = cache.head_dim;
+  if (head >= n_q_heads + (write_kv ? 2 * n_kv : 0)) return;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  const bool is_q = head < n_q_heads;
+  const bool is_k = !is_q && head < n_q_heads + n_kv;
+  const int kv_head = is_q ? 0 : (is_k ? head - n_q_heads : head - n_q_heads - n_kv);
+  T* src = rows + (size_t)t * row_stride + (is_q ? (size_t)head * d : (size_t)(is_k ? k_col : v_col) + (size_t)kv_head * d);
+  T* dst = src;
+  if (!is_q) {
+    const int page = cache.block_table[(size_t)token_slot[t] * cache.table_stride + pos / EK_PAGE];
+    dst = (T*)(is_k ? cache.k : cache.v) + page_offset(cache, page, kv_head, pos);
+  }
+  if (!is_q && !is_k) {                         // values: a copy
+    for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    return;
+  }
+  for (int i = lane; i < d; i += 32) buf[warp][i] = to_f<T>(src[i]);
+  __syncwarp();
+  const int half = rot_dim >> 1;
+  const float* cs = cos_tab + (size_t)pos * half;
+  const float* sn = sin_tab + (size_t)pos * half;
+  float y[EK_MAX_HEAD_DIM / 32];
+  float ss = 0.f;
+#pragma unroll
+  for (int r = 0; r < EK_MAX_HEAD_DIM / 32; ++r) {
+    const int i = lane + 32 * r;
+    float v = 0.f;
+    if (i < d) {
+      v = buf[warp][i];
+      if (i < half) v = v * cs[i] - buf[warp][i + half] * sn[i];
+      else if (i < rot_dim) v = v * cs[i - half] + buf[warp][i - half] * sn[i - half];
+    }
+    y[r] = v;
+    ss += v * v;
+  }
+  float rstd = 1.f;
+  if (unit) rstd = rsqrtf(warp_sum(ss) / (float)norm_dim + eps);
+#pragma unroll
+  for (int r = 0; r < EK_MAX_HEAD_DIM / 32; ++r) {
+    const int i = lane + 32 * r;
+    if (i < d) dst[i] = from_f<T>(y[r] * rstd);
+  }
+}
+
 // Wide form for 16-bit rows whose head size is 64, 128 or 256 and fully rotated: a block takes
 // every head of one token, D/8 lanes a head.  A lane holds 4 neighbouring dimensions of the head's
 // first half and the 4 they turn with in the second half (two 8-byte loads, each a full 128-byte
@@ -500,6 +562,28 @@ static int launch(void* qkv, int row_stride, const float* q_gain, const float* k
     return ek::launch<T>(qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, positions, \
                          token_slot, k_pages, v_pages, block_table, table_stride, n_tokens,    \
                          n_q_heads, n_kv_heads, head_dim, eps, write_kv, ex, stream);          \
+  }                                                                                            \
+  /* Rotation, then every query and key head over its root mean square (no gain); the row    */ \
+  /* holds query heads from column 0, key heads from k_col, value heads from v_col.          */ \
+  EK_EXPORT int ek_qk_rope_unit_kv_##SUFFIX(                                                    \
+      void* rows, int row_stride, int k_col, int v_col, const float* cos_tab,                  \
+      const float* sin_tab, int rot_dim, const int* positions, const int* token_slot,          \
+      void* k_pages, void* v_pages, const int* block_table, int table_stride, int n_tokens,    \
+      int n_q_heads, int n_kv_heads, int head_dim, int norm_dim, float eps, int unit,          \
+      int write_kv, cudaStream_t stream) {                                                     \
+    using namespace ek;                                                                        \
+    if (n_tokens <= 0) return 0;                                                               \
+    if (head_dim <= 0 || head_dim > EK_MAX_HEAD_DIM || rot_dim < 0 || rot_dim % 2 ||           \
+        rot_dim > head_dim || norm_dim <= 0 || norm_dim > head_dim || n_q_heads <= 0 ||        \
+        n_kv_heads <= 0)                                                                       \
+      return EK_ERR_ARG;                                                                       \
+    PagedKV cache{k_pages, v_pages, block_table, table_stride, n_kv_heads, head_dim};          \
+    const int heads = n_q_heads + (write_kv ? 2 * n_kv_heads : 0);                             \
+    dim3 grid(n_tokens, (heads + kRopeWarps - 1) / kRopeWarps);                                \
+    return (int)launch_pdl(qk_rope_unit_kv_kernel<T>, grid, dim3(kRopeWarps * 32), 0, stream,  \
+                           (T*)rows, row_stride, k_col, v_col, cos_tab, sin_tab, rot_dim,      \
+                           positions, token_slot, cache, n_q_heads, norm_dim, eps, unit,       \
+                           write_kv);                                                          \
   }
 
 EK_INSTANTIATE(f32, float)

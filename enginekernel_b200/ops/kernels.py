@@ -151,6 +151,57 @@ def rmsnorm(y, resid, gain, eps, add=None, rows=None, n_rows=None, write_back=Tr
                       n_rows, hidden, 1 if write_back else 0, _stream())
 
 
+_rmsnorm_scaled_sum = _per_dtype("elementwise", "ek_rmsnorm_scaled_sum",
+                                 [_P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, _P])
+
+
+def rmsnorm_scaled_sum(y, resid, a, gain, eps, scale_a=None, b=None, scale_b=None, rows=None, n_rows=None,
+                       write_back=True):
+    """stream += a * scale_a + b * scale_b (element by element; the scales are 32-bit vectors of the
+    stream's width, absent: ones; ``b`` may be absent), then y = gain * n(stream).  ``rows`` (int32)
+    picks stream rows (and the same rows of ``a`` and ``b``); y then has one row per entry."""
+    _need_cuda(y, resid, a, gain, scale_a, b, scale_b, rows)
+    hidden = resid.shape[-1]
+    _need(resid.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == hidden
+          and y.shape[-1] == hidden and y.is_contiguous() and resid.is_contiguous(),
+          "rmsnorm_scaled_sum: 32-bit stream and gain of one width")
+    for t in (a, b):
+        _need(t is None or (t.dtype == y.dtype and t.shape[-1] == hidden and t.is_contiguous()),
+              "rmsnorm_scaled_sum: the summands have y's dtype and the stream's width")
+    for t in (scale_a, scale_b):
+        _need(t is None or (t.dtype == torch.float32 and t.numel() == hidden and t.is_contiguous()),
+              "rmsnorm_scaled_sum: 32-bit scales of the stream's width")
+    _need(a is not None and (b is not None or scale_b is None), "rmsnorm_scaled_sum: a scale without its summand")
+    if n_rows is None:
+        n_rows = rows.numel() if rows is not None else resid.shape[0]
+    _need(y.shape[0] >= n_rows, "rmsnorm_scaled_sum: y has too few rows")
+    if lib.recording():
+        lib.annotate(bytes=n_rows * hidden * (4 + (4 if write_back else 0)
+                                              + y.element_size() * (2 if b is None else 3)))
+    _rmsnorm_scaled_sum[y.dtype](_ptr(y), _ptr(resid), _ptr(a), _ptr(scale_a), _ptr(b), _ptr(scale_b), _ptr(gain),
+                                 _ptr(rows), float(eps), n_rows, hidden, 1 if write_back else 0, _stream())
+
+
+_add_scaled = _per_dtype("elementwise", "ek_add_scaled", [_P, _P, _P, _P, _P, c_longlong, c_int, _P])
+
+
+def add_scaled(resid, a, scale_a=None, b=None, scale_b=None, n_rows=None):
+    """stream += a * scale_a + b * scale_b, element by element, without a norm (scales: 32-bit vectors of
+    the stream's width, absent: ones; ``b`` may be absent)."""
+    _need_cuda(resid, a, scale_a, b, scale_b)
+    hidden = resid.shape[-1]
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and a.is_contiguous() and a.shape[-1] == hidden
+          and (b is None or (b.dtype == a.dtype and b.is_contiguous() and b.shape[-1] == hidden)),
+          "add_scaled: 32-bit stream, summands of its width")
+    for t in (scale_a, scale_b):
+        _need(t is None or (t.dtype == torch.float32 and t.numel() == hidden and t.is_contiguous()),
+              "add_scaled: 32-bit scales of the stream's width")
+    n = (n_rows if n_rows is not None else resid.shape[0]) * hidden
+    if lib.recording():
+        lib.annotate(bytes=n * (8 + a.element_size() * (1 if b is None else 2)))
+    _add_scaled[a.dtype](_ptr(resid), _ptr(a), _ptr(scale_a), _ptr(b), _ptr(scale_b), n, hidden, _stream())
+
+
 def add_residual(resid, x, n_rows=None):
     _need_cuda(resid, x)
     n = (n_rows if n_rows is not None else resid.shape[0]) * resid.shape[-1]
@@ -256,10 +307,40 @@ def qk_norm_rope_kv(qkv, n_tokens, q_gain, k_gain, cos, sin, rot_dim, positions,
                         head_dim, float(eps), 1 if write_kv else 0, _stream())
 
 
+_rope_unit_kv = _per_dtype("rope_kv", "ek_qk_rope_unit_kv",
+                           [_P, c_int, c_int, c_int, _P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int,
+                            c_int, c_int, c_int, c_int, c_float, c_int, c_int, _P])
+
+
+def qk_rope_unit_kv(rows, n_tokens, k_col, v_col, cos, sin, rot_dim, positions, token_slot, k_pages, v_pages,
+                    block_table, n_q_heads, n_kv_heads, head_dim, norm_dim, eps, unit=True, write_kv=True):
+    """Rotation first, then every query and key head divided by its root mean square over its first
+    ``norm_dim`` values (no gain; ``unit`` False: rotation alone).  ``rows`` [T, .] holds a token's
+    query heads from column 0 (in place), and - read only when ``write_kv`` - its key heads from
+    ``k_col`` and value heads from ``v_col``, each ``head_dim`` apart; keys and values go to the pages."""
+    _need_cuda(rows, cos, sin, positions, token_slot, k_pages, v_pages, block_table)
+    check_head_dim(head_dim)
+    _need(rows.stride(-1) == 1 and rows.shape[-1] >= n_q_heads * head_dim, "qk_rope_unit_kv: row width")
+    _need(not write_kv or (k_col + n_kv_heads * head_dim <= rows.shape[-1]
+                           and v_col + n_kv_heads * head_dim <= rows.shape[-1]),
+          "qk_rope_unit_kv: key and value columns lie within the row")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+          and sin.is_contiguous() and cos.shape[-1] * 2 == rot_dim, "qk_rope_unit_kv: 32-bit tables of rot_dim/2 columns")
+    _need(k_pages.dtype == rows.dtype and v_pages.dtype == rows.dtype, "qk_rope_unit_kv: cache dtype")
+    _need(block_table.dtype == torch.int32 and positions.dtype == torch.int32
+          and token_slot.dtype == torch.int32, "qk_rope_unit_kv: int32 indices")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * head_dim * rows.element_size() * (2 * n_q_heads + (4 * n_kv_heads if write_kv else 0)))
+    _rope_unit_kv[rows.dtype](_ptr(rows), rows.stride(0), k_col, v_col, _ptr(cos), _ptr(sin), rot_dim,
+                              _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                              block_table.stride(0), n_tokens, n_q_heads, n_kv_heads, head_dim, norm_dim,
+                              float(eps), 1 if unit else 0, 1 if write_kv else 0, _stream())
+
+
 # ------------------------------------------------------------------ attention
 _attn_generic = _per_dtype("attention_generic", "ek_attention_generic",
                            [_P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
-                            c_float, c_int, c_int, c_int, _P, _P, c_float, _P, _P])
+                            c_float, c_int, c_int, c_int, _P, _P, c_float, _P, c_int, _P, c_int, _P])
 _NO_SINK = float("-inf")
 
 
@@ -280,7 +361,8 @@ def _sinks(sinks, n_q_heads):
 
 def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table,
                       n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1,
-                      keys_per_split=0, part_acc=None, part_ml=None, sink=None, sinks=None):
+                      keys_per_split=0, part_acc=None, part_ml=None, sink=None, sinks=None, keep_first=0,
+                      gate=None):
     """out[t, h*D:(h+1)*D] = softmax(scale q.K^T) V over the keys token t may see.  ``sink``: the
     score of one more key without a value that every query sees - exp(sink) is added to the
     softmax denominator (the same in every attention kernel below).  ``sinks`` [NQ] (32-bit):
@@ -289,8 +371,13 @@ def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages,
     ``q`` is any tensor whose row t starts with the NQ*D query values (the fused q/k/v
     rows qualify).  With ``n_splits`` > 1 the keys are cut every ``keys_per_split`` and
     merged from ``part_acc`` [T, NQ, splits, D] / ``part_ml`` [T, NQ, splits, 2] (32-bit).
+    ``keep_first`` (with a window): the first ``keep_first`` positions of a sequence stay visible to
+    every later token beside its window.  ``gate`` [T, >= NQ] (rows may be a view into wider rows):
+    head h's output at token t is multiplied by sigmoid(gate[t, h]).
     """
-    _need_cuda(out, q, positions, token_slot, k_pages, v_pages, block_table, part_acc, part_ml)
+    _need_cuda(out, q, positions, token_slot, k_pages, v_pages, block_table, part_acc, part_ml, gate)
+    _need(gate is None or (gate.dtype == q.dtype and gate.stride(-1) == 1 and gate.shape[-1] >= n_q_heads),
+          "attention: the gate holds one value per token and query head, in q's dtype")
     _need(1 <= head_dim <= GENERIC_MAX_HEAD_DIM, f"attention_generic: head sizes up to {GENERIC_MAX_HEAD_DIM}")
     _need(out.dtype == q.dtype == k_pages.dtype, "attention: one dtype for q, cache and out")
     _need(out.is_contiguous() and out.shape[-1] == n_q_heads * head_dim, "attention: out [T, NQ*D]")
@@ -304,7 +391,8 @@ def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages,
                            _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
                            n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale),
                            int(window or 0), n_splits, keys_per_split, _ptr(part_acc),
-                           _ptr(part_ml), _sink(sink), _sinks(sinks, n_q_heads), _stream())
+                           _ptr(part_ml), _sink(sink), _sinks(sinks, n_q_heads), int(keep_first or 0),
+                           _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
     if n_splits > 1:
         count_extra_launches()               # the merge kernel
 
@@ -1166,13 +1254,144 @@ def delta_out_norm(y, o, gate, w, eps, positions, n_tokens, shape):
                              _ptr(positions), n_tokens, *[int(v) for v in shape], _stream())
 
 
+# ------------------------------------------------------------------ linear recurrences with a decay per head
+_conv_silu = Function("recurrent", "ek_conv_silu",
+                      [_P, c_int, _P, c_int, c_int, _P, _P, _P, c_longlong, c_longlong, _P, _P, c_int, c_int, c_int, _P])
+_conv_tail = Function("recurrent", "ek_conv_tail",
+                      [_P, c_longlong, c_longlong, _P, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, _P])
+_ssm_gates = Function("recurrent", "ek_ssm_gates", [_P, _P, _P, c_int, c_int, _P, _P, c_int, c_int, _P])
+_xgate_scan = Function("recurrent", "ek_xgate_scan",
+                       [_P, _P, _P, _P, c_int, c_int, c_int, _P, _P, c_float, _P, c_longlong, c_longlong, _P, _P, _P,
+                        c_int, c_int, c_int, _P])
+_decay_scan = Function("recurrent", "ek_decay_scan",
+                       [_P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, c_longlong, _P, _P, _P,
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P])
+_ssm_out = _per_dtype("recurrent", "ek_ssm_out",
+                      [_P, _P, _P, c_int, _P, c_int, c_int, _P, _P, c_float, _P, c_int, c_int, c_int, c_int, _P])
+_xlstm_out = _per_dtype("recurrent", "ek_xlstm_out",
+                        [_P, _P, _P, _P, c_int, c_int, _P, c_float, c_float, _P, c_int, c_int, c_int, _P])
+DECAY_SCAN_MAX_KEY_DIM = 256
+
+
+def decay_scan_rows(dim: int) -> int:
+    """Rows of S per column that the decay scan keeps for keys of ``dim`` values (``dim`` rounded up to
+    32, 64, 128 or 256)."""
+    if not 0 < dim <= DECAY_SCAN_MAX_KEY_DIM:
+        raise KernelError(f"the decay scan takes key sizes up to {DECAY_SCAN_MAX_KEY_DIM}, not {dim}")
+    for rows in (32, 64, 128, 256):
+        if dim <= rows:
+            return rows
+
+
+def _need_f32(name, *tensors):
+    for t in tensors:
+        _need(t is None or (t.dtype == torch.float32 and t.stride(-1) == 1), f"{name}: 32-bit tensors")
+
+
+def conv_silu(out, proj, col0, conv_w, conv_b, state, tail_offset, positions, token_slot, n_tokens, channels, taps):
+    """out[t, c] = silu(b[c] + sum_j w[c, taps-1-j] x[t-j, c]) with x = proj[., col0 + c] (all 32-bit): a
+    causal convolution per channel whose last column multiplies the current token.  Tokens before the
+    step's first of a sequence come from the slot's state ([channels, taps-1] from ``tail_offset`` on,
+    oldest first; zeros for a new sequence)."""
+    _need_cuda(out, proj, conv_w, conv_b, state, positions, token_slot)
+    _need_f32("conv_silu", out, proj, conv_w, conv_b, state)
+    _need(conv_w.is_contiguous() and tuple(conv_w.shape) == (channels, taps) and out.shape[-1] >= channels
+          and col0 + channels <= proj.shape[-1], "conv_silu: weights [channels, taps], columns within the rows")
+    if lib.recording():
+        lib.annotate(bytes=8 * n_tokens * channels)
+    _conv_silu(_ptr(out), out.stride(0), _ptr(proj), proj.stride(0), col0, _ptr(conv_w), _ptr(conv_b), _ptr(state),
+               state.stride(0), tail_offset, _ptr(positions), _ptr(token_slot), n_tokens, channels, taps, _stream())
+
+
+def conv_tail(state, tail_offset, proj, col0, cu_seqlens, positions, token_slot, n_seqs, channels, taps):
+    """The last ``taps - 1`` convolution inputs of every sequence of the step go to its state."""
+    _need_cuda(state, proj, cu_seqlens, positions, token_slot)
+    _need_f32("conv_tail", state, proj)
+    _conv_tail(_ptr(state), state.stride(0), tail_offset, _ptr(proj), proj.stride(0), col0, _ptr(cu_seqlens),
+               _ptr(positions), _ptr(token_slot), n_seqs, channels, taps, _stream())
+
+
+def ssm_gates(a, b, proj, col0, dt_bias, a_log, n_tokens, heads):
+    """dt = softplus(proj[t, col0 + h] + dt_bias[h]); a[t, h] = exp(-exp(a_log[h]) dt), b[t, h] = dt."""
+    _need_cuda(a, b, proj, dt_bias, a_log)
+    _need_f32("ssm_gates", a, b, proj, dt_bias, a_log)
+    _need(a.is_contiguous() and b.is_contiguous() and a.shape[-1] == heads == b.shape[-1]
+          and dt_bias.numel() == heads == a_log.numel(), "ssm_gates: one value per head")
+    _ssm_gates(_ptr(a), _ptr(b), _ptr(proj), proj.stride(0), col0, _ptr(dt_bias), _ptr(a_log), n_tokens, heads,
+               _stream())
+
+
+def xgate_scan(a, b, m_run, proj, col_i, col_f, bias_i, bias_f, cap, state, m_offset, cu_seqlens, positions,
+               token_slot, n_seqs, heads, write_state=True):
+    """Exponential gates kept stable by a running maximum: i = cap tanh((x_i + b_i) / cap), f =
+    logsigmoid(cap tanh((x_f + b_f) / cap)), m_t = max(f + m_(t-1), i) continued from the slot's state
+    (``heads`` values from ``m_offset`` on); a = exp(f + m_(t-1) - m_t), b = exp(i - m_t), m_run = m_t."""
+    _need_cuda(a, b, m_run, proj, bias_i, bias_f, state, cu_seqlens, positions, token_slot)
+    _need_f32("xgate_scan", a, b, m_run, proj, bias_i, bias_f, state)
+    _need(a.is_contiguous() and b.is_contiguous() and m_run.is_contiguous() and a.shape[-1] == heads,
+          "xgate_scan: a, b, m [T, heads]")
+    _xgate_scan(_ptr(a), _ptr(b), _ptr(m_run), _ptr(proj), proj.stride(0), col_i, col_f, _ptr(bias_i), _ptr(bias_f),
+                float(cap), _ptr(state), state.stride(0), m_offset, _ptr(cu_seqlens), _ptr(positions),
+                _ptr(token_slot), n_seqs, heads, 1 if write_state else 0, _stream())
+
+
+def decay_scan(out, q, k, v, a, b, state, cu_seqlens, positions, token_slot, n_seqs, heads, kv_heads, dim, vdim,
+               ones_column=False, write_state=True, n_tokens=0):
+    """S_t = a_t S_(t-1) + b_t k_t v_t^T, out_t = S_t^T q_t per head over every sequence's tokens, S
+    ([heads, columns, rows] at the start of a slot's state, 32-bit) read and written back.  ``q``, ``k``
+    [T, >= kv_heads * dim] (head h reads key head h // (heads / kv_heads)), ``v`` [T, >= heads * vdim],
+    ``a``, ``b`` [T, heads].  ``ones_column``: one more column whose v is 1 (it carries a n + b k and
+    gives n . q); out is [T, heads * columns]."""
+    _need_cuda(out, q, k, v, a, b, state, cu_seqlens, positions, token_slot)
+    _need_f32("decay_scan", out, q, k, v, a, b, state)
+    cols = vdim + (1 if ones_column else 0)
+    _need(out.shape[-1] == heads * cols and a.is_contiguous() and b.is_contiguous() and a.shape[-1] == heads,
+          "decay_scan: out [T, heads * columns], a and b [T, heads]")
+    _need(state.stride(0) % 4 == 0 and state.shape[-1] >= heads * cols * decay_scan_rows(dim),
+          "decay_scan: the state holds S and every slot starts on a 16-byte boundary")
+    if lib.recording():
+        lib.annotate(bytes=4 * (n_tokens * (2 * kv_heads * dim + 2 * heads * vdim + 2 * heads)
+                                + 2 * n_seqs * heads * cols * decay_scan_rows(dim)),
+                     flops=4 * n_tokens * heads * dim * cols)
+    _decay_scan(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0),
+                _ptr(a), _ptr(b), _ptr(state), state.stride(0), _ptr(cu_seqlens), _ptr(positions), _ptr(token_slot),
+                n_seqs, heads, kv_heads, dim, vdim, 1 if ones_column else 0, 1 if write_state else 0, _stream())
+
+
+def ssm_out(y, o, x, proj, col_z, d_skip, w, eps, positions, n_tokens, inner, vdim, parts):
+    """y = n((o + D[head] x) silu(z)) w in the activation type, the norm over each of ``parts`` equal parts
+    of the ``inner`` channels; z = proj[., col_z + c], x [T, >= inner] the convolved inputs."""
+    _need_cuda(y, o, x, proj, d_skip, w, positions)
+    _need_f32("ssm_out", o, x, proj, d_skip, w)
+    _need(y.is_contiguous() and o.is_contiguous() and o.shape[-1] == inner == y.shape[-1] and w.numel() == inner,
+          "ssm_out: y, o [T, inner]")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * inner * (12 + y.element_size()))
+    _ssm_out[y.dtype](_ptr(y), _ptr(o), _ptr(x), x.stride(0), _ptr(proj), proj.stride(0), col_z, _ptr(d_skip),
+                      _ptr(w), float(eps), _ptr(positions), n_tokens, inner, vdim, parts, _stream())
+
+
+def xlstm_out(y, o, m_run, proj, col_g, w, eps, q_scale, positions, n_tokens, heads, vdim):
+    """``o`` [T, heads * (vdim + 1)] from the scan with n . q in each head's last column, both still to
+    be multiplied by ``q_scale``: u = o q_scale / (max(|n . q| q_scale, exp(-m)) + 1e-6); y = u / rms(u)
+    per head * w * sigmoid(proj[., col_g + c]) in the activation type."""
+    _need_cuda(y, o, m_run, proj, w, positions)
+    _need_f32("xlstm_out", o, m_run, proj, w)
+    _need(y.is_contiguous() and o.is_contiguous() and m_run.is_contiguous() and y.shape[-1] == heads * vdim
+          and o.shape[-1] == heads * (vdim + 1) and w.numel() == heads * vdim, "xlstm_out: shapes")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * heads * vdim * (8 + y.element_size()))
+    _xlstm_out[y.dtype](_ptr(y), _ptr(o), _ptr(m_run), _ptr(proj), proj.stride(0), col_g, _ptr(w), float(eps),
+                        float(q_scale), _ptr(positions), n_tokens, heads, vdim, _stream())
+
+
 # ------------------------------------------------------------------ routed experts
-_moe_route = Function("moe", "ek_moe_route", [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P])
+_moe_route = Function("moe", "ek_moe_route", [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P])
 _moe_plan = Function("moe", "ek_moe_plan", [_P, _P, _P, _P, c_int, c_int, _P])
-_moe_up = _per_dtype("moe", "ek_moe_expert_up", [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P])
+_moe_up = _per_dtype("moe", "ek_moe_expert_up", [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P])
 _moe_down = _per_dtype("moe", "ek_moe_expert_down", [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P])
 _moe_combine = _per_dtype("moe", "ek_moe_combine", [_P, _P, c_int, c_int, c_int, _P])
-_moe_up_tc = Function("moe", "ek_moe_expert_up_tc", [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P])
+_moe_up_tc = Function("moe", "ek_moe_expert_up_tc", [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P])
 _moe_down_tc = Function("moe", "ek_moe_expert_down_tc", [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P])
 
 
@@ -1188,13 +1407,15 @@ def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
     return -(-n_pairs // MOE_TILE_ROWS) + min(n_experts, n_pairs)
 
 
-def moe_route(sel_expert, sel_weight, logits, n_tokens, n_groups, keep, top, scale):
-    """Router: ``logits`` [T, E] 32-bit -> the ``top`` chosen experts and their weights per token."""
+def moe_route(sel_expert, sel_weight, logits, n_tokens, n_groups, keep, top, scale, among_chosen=False):
+    """Router: ``logits`` [T, E] 32-bit -> the ``top`` chosen experts and their weights per token.
+    ``among_chosen``: the weights are the softmax over the chosen logits alone (times ``scale``)
+    instead of the chosen scores of the softmax over all experts, divided by their sum."""
     _need_cuda(sel_expert, sel_weight, logits)
     _need(logits.dtype == torch.float32 and logits.is_contiguous() and sel_expert.dtype == torch.int32
           and sel_weight.dtype == torch.float32, "moe_route: 32-bit logits and weights, int32 choices")
     _moe_route(_ptr(sel_expert), _ptr(sel_weight), _ptr(logits), n_tokens, logits.shape[-1], n_groups, keep,
-               top, float(scale), _stream())
+               top, float(scale), 1 if among_chosen else 0, _stream())
 
 
 def moe_plan(sorted_pair, tiles, n_tiles, sel_expert, n_pairs, n_experts):
@@ -1202,8 +1423,10 @@ def moe_plan(sorted_pair, tiles, n_tiles, sel_expert, n_pairs, n_experts):
     _moe_plan(_ptr(sorted_pair), _ptr(tiles), _ptr(n_tiles), _ptr(sel_expert), n_pairs, n_experts, _stream())
 
 
-def moe_expert_up(out, x, w, tiles, n_tiles, sorted_pair, n_pairs, top, activation):
-    """out[sorted row] = act(x[token of the pair] . w[expert]^T); ``w`` [E, N, K]."""
+def moe_expert_up(out, x, w, tiles, n_tiles, sorted_pair, n_pairs, top, activation, gated=False):
+    """out[sorted row] = act(x[token of the pair] . w[expert]^T); ``w`` [E, N, K].  ``gated``: the
+    rows of an expert's ``w`` alternate gate, up, gate, up ...; out [pairs, N / 2] holds
+    act(gate) * up, taken from the 32-bit sums."""
     _need_cuda(out, x, w, tiles, n_tiles, sorted_pair)
     _need(out.dtype == x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous() and out.is_contiguous(),
           "moe_expert_up: one dtype, contiguous")
@@ -1212,7 +1435,7 @@ def moe_expert_up(out, x, w, tiles, n_tiles, sorted_pair, n_pairs, top, activati
         lib.annotate(bytes=x.element_size() * (min(e, n_pairs) * n * k + n_pairs * (n + k)), flops=2 * n_pairs * n * k)
     fn = _moe_up_tc if _moe_on_tensor_cores(x, w) else _moe_up[x.dtype]
     fn(_ptr(out), _ptr(x), _ptr(w), _ptr(tiles), _ptr(n_tiles), _ptr(sorted_pair),
-       moe_max_tiles(n_pairs, e), top, n, k, EXPERT_ACTIVATIONS[activation], _stream())
+       moe_max_tiles(n_pairs, e), top, n, k, EXPERT_ACTIVATIONS[activation], 1 if gated else 0, _stream())
 
 
 def moe_expert_down(pair_out, a, w, tiles, n_tiles, sorted_pair, pair_weight, n_pairs):

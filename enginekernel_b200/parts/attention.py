@@ -23,6 +23,21 @@ Optional parameters, all off by default, for designs that differ there:
                        1 + coef * ln(floor((p + 1) / every) + 1).
 ``sink``               the score of one more key without a value that every query sees: its
                        exponential is one more term of the softmax denominator (0.0: "+ 1").
+``value_dim``          size of a value head when it differs from ``head_dim`` (``v`` is then [NKV * E, H]
+                       and ``o`` [H, NH * E]); the cache and the kernels see heads of the larger of the
+                       two sizes (rounded up to 8 values), the shorter ones padded with zeros.
+``unit_norm_after_rotation``  an eps: queries and keys are rotated first and then divided by their root
+                       mean square over the head (no gain), instead of the gained norm before rotation.
+``keep_first``         with a window: the first ``keep_first`` positions of a sequence stay visible to every
+                       later token, at their true positions.  The cache then keeps all keys.
+``head_gate``          every head's output is multiplied by the sigmoid of one number per token and head,
+                       a projection of the mixer's input (tensor ``gate`` [NH, H]), before ``o``.
+``kv_projection``      False: the layer has no ``k`` and ``v``; it reads the keys and values another run
+                       stored in the cache entry it shares (a run with ``writes_cache=False``).
+``keep_all_keys``      the cache keeps every key although this layer sees a window (layers that share an
+                       entry may see different windows).
+Any of these sends the layer down one path: a single product for everything that reads the input,
+the rotate-and-norm kernel, and the general attention kernel.
 """
 
 from __future__ import annotations
@@ -45,10 +60,15 @@ class Attention(Mixer):
     def tensors(cls, spec):
         p, w = spec.params, spec.weights
         h, nh, nkv, d = p["hidden_size"], p["num_heads"], p["num_kv_heads"], p["head_dim"]
-        out = [TensorSpec(w["q"], (nh * d, h)), TensorSpec(w["k"], (nkv * d, h))]
-        if p.get("values", "projection") != "keys":
-            out.append(TensorSpec(w["v"], (nkv * d, h)))
-        out.append(TensorSpec(w["o"], (h, nh * d)))
+        e = int(p.get("value_dim") or d)
+        out = [TensorSpec(w["q"], (nh * d, h))]
+        if p.get("kv_projection", True):
+            out.append(TensorSpec(w["k"], (nkv * d, h)))
+            if p.get("values", "projection") != "keys":
+                out.append(TensorSpec(w["v"], (nkv * e, h)))
+        if p.get("head_gate"):
+            out.append(TensorSpec(w["gate"], (nh, h)))
+        out.append(TensorSpec(w["o"], (h, nh * e)))
         if p.get("qk_norm_eps") is not None:
             out += [TensorSpec(w["q_norm"], (d,), "gain"), TensorSpec(w["k_norm"], (d,), "gain")]
         for which in p.get("bias") or ():
@@ -78,12 +98,34 @@ class Attention(Mixer):
         if self.num_heads % self.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         kernels.check_head_dim(self.head_dim)
+        self.value_dim = int(spec.params.get("value_dim") or self.head_dim)
+        self.unit_norm_eps = spec.params.get("unit_norm_after_rotation")
+        self.keep_first = int(spec.params.get("keep_first") or 0)
+        self.head_gate = bool(spec.params.get("head_gate"))
+        self.kv_projection = bool(spec.params.get("kv_projection", True))
+        self.keep_all_keys = bool(spec.params.get("keep_all_keys")) or self.keep_first > 0
+        self.general = (self.value_dim != self.head_dim or self.unit_norm_eps is not None or self.keep_first > 0
+                        or self.head_gate or not self.kv_projection)
+        #: the head size the cache and the kernels see
+        self.padded_dim = self.head_dim
+        if self.general:
+            if not self._plain or self.qk_norm_eps is not None or self.sink is not None:
+                raise ValueError("attention: value_dim, unit_norm_after_rotation, keep_first, head_gate and "
+                                 "kv_projection do not combine with biases, values from keys, a query "
+                                 "temperature, the gained q/k norm or a sink")
+            if self.keep_first and not self.window:
+                raise ValueError("attention: keep_first needs a window")
+            self.padded_dim = -(-max(self.head_dim, self.value_dim) // 8) * 8
+            kernels.check_head_dim(self.padded_dim)
+            # (this path takes normalised activations and returns a plain tensor)
+            self.takes_deferred_norm = self.defers_norm = False
         pos = spec.params.get("position")
         self.position = lookup_part("position", pos.kind)(pos, dtype, device) if pos else None
         self.w_qkv = self.w_o = self.q_gain = self.k_gain = None
 
     def cache_spec(self):
-        return CacheSpec("kv", heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window)
+        return CacheSpec("kv", heads=self.num_kv_heads, head_dim=self.padded_dim,
+                         window=None if self.keep_all_keys else self.window)
 
     def prepare(self, max_positions):
         if self.position is not None:
@@ -94,7 +136,7 @@ class Attention(Mixer):
 
     def begin_step(self, ctx):
         """The table of tiles of the tcgen05 prompt attention, once per step and shape of the heads."""
-        if ctx.is_decode or ctx.n_seqs > kernels.PREFILL_TC_MAX_SEQS or not self.scale > 0 or \
+        if self.general or ctx.is_decode or ctx.n_seqs > kernels.PREFILL_TC_MAX_SEQS or not self.scale > 0 or \
                 not kernels.attention_prefill_tc_supported(self.dtype, self.head_dim, self.num_heads,
                                                            self.num_kv_heads):
             return
@@ -108,7 +150,69 @@ class Attention(Mixer):
                                             ctx.n_seqs, self.num_heads, self.num_kv_heads, self.head_dim)
         ctx.shared[key] = (tiles, n)
 
+    def _load_general(self, tensors):
+        """[q | k | v | gate] as one weight, every head padded with zero rows to ``padded_dim``, zero rows
+        up to a multiple of 64; ``o`` with zero columns where the value heads are padded."""
+        w, big = self.spec.weights, self.padded_dim
+
+        def heads(t, n, size):
+            t = t.view(n, size, self.hidden)
+            if size == big:
+                return t.reshape(n * big, self.hidden)
+            out = torch.zeros((n, big, self.hidden), dtype=t.dtype, device=t.device)
+            out[:, :size] = t
+            return out.view(n * big, self.hidden)
+
+        rows = [heads(tensors[w["q"]], self.num_heads, self.head_dim)]
+        if self.kv_projection:
+            rows += [heads(tensors[w["k"]], self.num_kv_heads, self.head_dim),
+                     heads(tensors[w["v"]], self.num_kv_heads, self.value_dim)]
+        if self.head_gate:
+            rows.append(tensors[w["gate"]])
+        n = sum(r.shape[0] for r in rows)
+        if n % 64:
+            rows.append(torch.zeros((-n % 64, self.hidden), dtype=rows[0].dtype, device=rows[0].device))
+        self.w_qkv = torch.cat(rows, dim=0).to(self.dtype).contiguous()
+        o = tensors[w["o"]].view(self.hidden, self.num_heads, self.value_dim)
+        if self.value_dim != big:
+            wide = torch.zeros((self.hidden, self.num_heads, big), dtype=o.dtype, device=o.device)
+            wide[:, :, :self.value_dim] = o
+            o = wide
+        self.w_o = o.reshape(self.hidden, self.num_heads * big).to(self.dtype).contiguous()
+
+    def _forward_general(self, x, ctx, entry, writes_cache):
+        t, big, nh, nkv = ctx.n_tokens, self.padded_dim, self.num_heads, self.num_kv_heads
+        pos = self.position
+        rows = linear(x, self.w_qkv, ctx, "qkv", n_rows=t)
+        k_col = nh * big
+        gate_col = k_col + (2 * nkv * big if self.kv_projection else 0)
+        kernels.qk_rope_unit_kv(
+            rows, t, k_col, k_col + nkv * big, pos.cos if pos else _no_table(self.device),
+            pos.sin if pos else _no_table(self.device), pos.rotary_dim if pos else 0, ctx.positions,
+            ctx.token_slot, entry.k_pages, entry.v_pages, entry.block_table, nh, nkv, big, self.head_dim,
+            self.unit_norm_eps or 0.0, unit=self.unit_norm_eps is not None,
+            write_kv=writes_cache and self.kv_projection)
+        out = ctx.workspace.get("attn_out", (t, nh * big), self.dtype)
+        visible = min(ctx.max_context, self.window + self.keep_first) if self.window else ctx.max_context
+        splits, per_split, acc, ml = 1, 0, None, None
+        blocks = t * nh
+        if blocks < 2 * kernels.sm_count(self.device) and visible > 512:
+            splits = max(1, min(-(-visible // 256), -(-4 * kernels.sm_count(self.device) // blocks), 64))
+        if splits > 1:
+            per_split = -(-(-(-ctx.max_context // splits)) // 128) * 128
+            splits = -(-ctx.max_context // per_split)
+        if splits > 1:
+            acc = ctx.workspace.get("attn_part_acc", (t, nh, splits, big), torch.float32)
+            ml = ctx.workspace.get("attn_part_ml", (t, nh, splits, 2), torch.float32)
+        kernels.attention_generic(out, rows, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
+                                  entry.block_table, nh, nkv, big, self.scale, self.window, splits, per_split,
+                                  acc, ml, keep_first=self.keep_first,
+                                  gate=rows[:, gate_col:] if self.head_gate else None)
+        return linear(out, self.w_o, ctx, "attn_proj", n_rows=t)
+
     def load(self, tensors):
+        if self.general:
+            return self._load_general(tensors)
         w = self.spec.weights
         rows = [tensors[w["q"]], tensors[w["k"]]] + ([] if self.values_from_keys else [tensors[w["v"]]])
         self.w_qkv = torch.cat(rows, dim=0).to(self.dtype).contiguous()
@@ -130,6 +234,10 @@ class Attention(Mixer):
     def forward(self, x, ctx, entry, writes_cache=True, defer=None):
         t = ctx.n_tokens
         pos = self.position
+        if self.general:
+            if isinstance(x, DeferredNorm):
+                raise kernels.KernelError("this attention layer takes normalised activations, not a deferred norm")
+            return self._forward_general(x, ctx, entry, writes_cache)
         if self._fuses_rope(x, ctx):
             # few rows, heads of 128: norm, rotation and cache write ride on the product's epilogue
             row_scale, xin = (row_scale_of(x), x.scaled) if isinstance(x, DeferredNorm) else (None, x)

@@ -56,6 +56,8 @@ class RopeStretched(PositionEncoding):
     max(hi - lo, 0.001), 0, 1).  Dimension i turns by position * (f_i / factor * ramp_i + f_i (1 - ramp_i)),
     and cosines and sines are multiplied by 0.1 ln(factor) + 1.  Parameters: ``rotary_dim`` (rot),
     ``theta``, and ``factor``, ``original``, ``fast``, ``slow`` (without ``factor``: the plain rotation).
+    With ``divide`` every frequency is divided by that number afterwards (positions interpolated
+    linearly; it works without ``factor`` too).
     The tables are worked out in 64-bit on the host and kept in 32-bit, with the factor on cos and sin
     folded in, so the kernels that read ``cos`` / ``sin`` need to know nothing of it.
     """
@@ -65,6 +67,9 @@ class RopeStretched(PositionEncoding):
         self.rotary_dim = int(self.param("rotary_dim"))
         self.theta = float(self.param("theta"))
         self.factor = spec.params.get("factor")
+        self.divide = float(spec.params.get("divide") or 1.0)
+        if not self.divide > 0:
+            raise ValueError("rope_stretched: divide must be positive")
         if self.rotary_dim % 2 or self.rotary_dim < 0:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even")
         if self.factor is not None:
@@ -82,6 +87,7 @@ class RopeStretched(PositionEncoding):
         rot, half = self.rotary_dim, self.rotary_dim // 2
         i = torch.arange(half, dtype=torch.float64)
         f = self.theta ** (-2.0 * i / max(rot, 1))
+        f = f / self.divide
         if self.factor is None:
             return f, 1.0
 
@@ -94,7 +100,7 @@ class RopeStretched(PositionEncoding):
         return f / self.factor * ramp + f * (1.0 - ramp), 0.1 * math.log(self.factor) + 1.0
 
     def prepare(self, max_positions: int) -> None:
-        key = ("stretched", str(self.device), self.theta, self.rotary_dim, max_positions, self.factor,
+        key = ("stretched", str(self.device), self.theta, self.rotary_dim, max_positions, self.factor, self.divide,
                getattr(self, "original", None), getattr(self, "fast", None), getattr(self, "slow", None))
         if key not in _TABLES:
             f, mult = self.frequencies()
