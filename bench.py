@@ -4,6 +4,7 @@
                     [--batch B] [--layers L] [--skip-points] [--skip-kernels]
     python bench.py --design lopazen [--sizes 0.6b,4b,1b-h64] [--layers L] [--batch B] [--skip-kernels]
     python bench.py --design susalorn [--sizes 1b,2b-dense] [--layers L] [--batch B] [--skip-kernels]
+    python bench.py --design bolelix [--sizes 1b,2b] [--layers L] [--batch B] [--skip-kernels]
 
 The shapes and workloads are the ones BASELINE.json names (its configs[2], [3], [4]):
 
@@ -27,6 +28,9 @@ beside the Qwen3 decoder at equal layer sizes (12 layers unless ``--layers`` say
 ``--design susalorn`` does the same for the Susalorn decoder (alternating latent-attention and
 delta-rule layers over four residual streams, routed or dense feed-forwards) beside a Qwen3 decoder
 of the same width, layer count and feed-forward work per token.
+``--design bolelix`` measures the Bolelix decoder (state-space, windowed-attention and matrix-memory layers in
+turn, every one with gated routed experts beside the mixer) next to the Susalorn decoder of the same width, layer
+count and experts.
 One line of JSON is printed.  The inputs of a step (gigabytes of weights) are larger than
 the L2.
 
@@ -383,7 +387,54 @@ def susalorn_configs(size: dict, layers: int, context: int):
     return susalorn, qwen3
 
 
-DESIGNS = {"lopazen": (DESIGN_SIZES, design_configs), "susalorn": (SUSALORN_SIZES, susalorn_configs)}
+# Bolelix at sizes that resemble real layers, beside the Susalorn decoder - the closest design here: it too has
+# a recurrent mixer over a per-sequence state, attention layers and routed experts - at the same width, layer
+# count, head sizes and experts.  Layers in turn: state-space, attention with a window and kept first tokens,
+# matrix memory, attention reading the keys of the attention layer before it.
+BOLELIX_SIZES = {
+    "1b": dict(width=2048, vocab=128256,
+               attention=dict(heads=16, kv_heads=8, dim=128, vdim=128, rot=64, window=1024, keep_first=4),
+               mamba2=dict(heads=32, vdim=128, state=128, groups=8, conv=4, norm_groups=8),
+               mlstm=dict(heads=16, dim=128, vdim=128, gate_cap=15.0),
+               moe=dict(experts=32, ff=1024, top=4), beside=dict(SUSALORN_SIZES["1b"])),
+    "2b": dict(width=2560, vocab=151936,
+               attention=dict(heads=20, kv_heads=10, dim=128, vdim=128, rot=128, window=512, keep_first=64),
+               mamba2=dict(heads=40, vdim=128, state=128, groups=4, conv=4, norm_groups=1),
+               mlstm=dict(heads=20, dim=128, vdim=128, gate_cap=15.0),
+               moe=dict(experts=16, ff=1536, top=2),
+               beside=dict(width=2560, vocab=151936,
+                           latent=dict(heads=20, dim=128, rot_dim=64, vdim=128, q_rank=1024, kv_rank=192),
+                           delta=dict(heads=20, kv_heads=10, dim=128, vdim=128, conv=4, rank=80),
+                           moe=dict(experts=16, ff=1536, top=2, groups=(4, 2)),
+                           qwen3=dict(heads=20, kv_heads=10, dim=128, ff=2048))),
+}
+
+
+def bolelix_configs(size: dict, layers: int, context: int):
+    """(Bolelix configuration, Susalorn configuration) of one size."""
+    from enginekernel_b200.config import BolelixConfig
+    at, m = size["attention"], size["moe"]
+    mlp = {"kind": "moe", "expert": {"ff": m["ff"]}, "router": {"experts": m["experts"], "top": m["top"]}}
+    attn = {"dim": at["dim"], "vdim": at["vdim"], "heads": at["heads"], "kv_heads": at["kv_heads"],
+            "scale": at["dim"] ** -0.5 * 8.0, "rot": {"base": 1000000.0, "dims": at["rot"], "scaling": {"factor": 4.0}},
+            "mask": {"size": at["window"], "keep_first": at["keep_first"]}}
+    made = []
+    for i in range(layers):
+        kind = i % 4
+        if kind == 0:
+            made.append({"type": "mamba2", "mixer": dict(size["mamba2"]), "mlp": mlp})
+        elif kind == 2:
+            made.append({"type": "mlstm", "mixer": dict(size["mlstm"]), "mlp": mlp})
+        else:
+            made.append({"type": "attention", "mixer": dict(attn, **({"kv_from": i - 2} if kind == 3 else {})), "mlp": mlp})
+    bolelix = BolelixConfig.from_dict({"architecture": "Bolelix", "vocab": size["vocab"], "width": size["width"],
+                                       "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "layers": made})
+    return bolelix, susalorn_configs(size["beside"], layers, context)[0]
+
+
+#: design -> (sizes, configurations of one size, the design it is measured beside)
+DESIGNS = {"lopazen": (DESIGN_SIZES, design_configs, "qwen3"), "susalorn": (SUSALORN_SIZES, susalorn_configs, "qwen3"),
+           "bolelix": (BOLELIX_SIZES, bolelix_configs, "susalorn")}
 
 
 def measure_design(cfg, vocab, batch, prompt_len, context, steps, warmup, pk, with_kernels):
@@ -473,19 +524,19 @@ def run_designs(args) -> int:
     sampler = ClockSampler()
     sampler.start()
     sizes = {}
-    design_sizes, make_configs = DESIGNS[args.design]
+    design_sizes, make_configs, beside = DESIGNS[args.design]
     for name in (args.sizes.split(",") if args.sizes else list(design_sizes)):
         size = design_sizes[name]
-        design, qwen3 = make_configs(size, layers, context)
+        design, other = make_configs(size, layers, context)
         sizes[name] = {"size": size, "layers": layers}
-        for tag, cfg in ((args.design, design), ("qwen3", qwen3)):
+        for tag, cfg in ((args.design, design), (beside, other)):
             sizes[name][tag] = measure_design(cfg, size["vocab"], batch, prompt_len, context, steps,
                                               max(3, args.warmup), pk, not args.skip_kernels)
-        a, b = sizes[name][args.design], sizes[name]["qwen3"]
-        sizes[name][args.design + "_over_qwen3"] = {"prefill_tok_s": a["prefill_tok_s"] / b["prefill_tok_s"],
-                                                    "decode_tok_s": a["decode_tok_s"] / b["decode_tok_s"]}
+        a, b = sizes[name][args.design], sizes[name][beside]
+        sizes[name][f"{args.design}_over_{beside}"] = {"prefill_tok_s": a["prefill_tok_s"] / b["prefill_tok_s"],
+                                                       "decode_tok_s": a["decode_tok_s"] / b["decode_tok_s"]}
     print(json.dumps({
-        "design": args.design, "beside": "qwen3", "dtype": "bf16", "n_gpus": 1,
+        "design": args.design, "beside": beside, "dtype": "bf16", "n_gpus": 1,
         "data": "synthetic: seeded random weights and uniform random token ids",
         "workload": {"batch": batch, "prompt_tokens": prompt_len, "context": context, "decode_steps": f"median of 5 stretches of {steps}",
                      "prefill": "one prompt of 2,048 tokens in one step", "timing": "CUDA events",
@@ -509,9 +560,9 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-kernels", action="store_true", help="leave out the per-kernel tables")
     ap.add_argument("--prefill-seqs", type=int, default=1,
                     help="sequences of 2,048 tokens in the prompt step of the per-kernel table")
-    ap.add_argument("--design", default="", choices=["", "lopazen", "susalorn"],
-                    help="instead of the default workload: this design beside the Qwen3 decoder at "
-                         "equal layer sizes (prompt step, decode step, per-kernel tables)")
+    ap.add_argument("--design", default="", choices=["", "lopazen", "susalorn", "bolelix"],
+                    help="instead of the default workload: this design beside the Qwen3 decoder (bolelix: beside "
+                         "the Susalorn decoder) at equal layer sizes (prompt step, decode step, per-kernel tables)")
     ap.add_argument("--sizes", default="", help="with --design: comma-separated names of DESIGN_SIZES")
     args = ap.parse_args(argv)
 

@@ -13,6 +13,10 @@
 //   * the 4 warps of a block take alternate 16-key units of the block's key range with
 //     their own running (max, sum, accumulator) and merge them in shared memory; blocks
 //     split long sequences (grid.z) into partials that a combine kernel merges in order.
+// `keep_first` > 0 (with a window): the first keep_first positions of the sequence stay visible beside
+// the window; their 16-key units are walked before the window's, by the first split.  `gate`, if given,
+// holds one value per token and query head (row stride `gate_stride`): the head's output is multiplied
+// by its sigmoid where the output is written.
 // The reference's counterpart is the Triton split-K flash-decoding kernel with the group
 // padded to 16 rows and tiles staged through shared memory (engine/ek_kernels.py:534-615,
 // combine 988-1019; split planning 1355-1381).  Softmax is computed in 32-bit.
@@ -59,7 +63,8 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
                              PagedKV cache, int n_q_heads, int row_blocks, float scale_log2,
                              int window, int n_splits, int keys_per_split,
                              float* __restrict__ part_acc, float* __restrict__ part_ml,
-                             float sink_log2, const float* __restrict__ sinks) {
+                             float sink_log2, const float* __restrict__ sinks, int keep_first,
+                             const bf16* __restrict__ gate, int gate_stride) {
   constexpr int D = DCH * 32;
   extern __shared__ float smem[];              // [warps][16][D] accumulators, then [warps][16][2]
   float* o_s = smem;
@@ -77,14 +82,18 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
   const int rows = min(16, group - rb * 16);               // real rows of this block
 
   int lo = 0, hi = -1;
+  int f_hi = -1;                               // kept first keys 0 .. f_hi, before the window
   if (pos >= 0) {
     lo = window > 0 ? max(0, pos - window + 1) : 0;
     hi = pos;
+    f_hi = min(keep_first, lo) - 1;
     if (n_splits > 1) {
       if (keys_per_split > 0) {                // fixed cut of the key axis
         lo = max(lo, split * keys_per_split);
         hi = min(hi, (split + 1) * keys_per_split - 1);
-      } else {                                 // cut this token's visible keys evenly
+        if (split > 0) f_hi = -1;              // (the kept keys lie within the first cut, or are left to it)
+      } else {
+        if (split > 0) f_hi = -1;              // cut this token's visible keys evenly
         const int first = lo & ~(kUnit - 1);
         const int per = max(kUnit, (((hi - first + n_splits) / n_splits) + kUnit - 1) & ~(kUnit - 1));
         lo = max(lo, first + split * per);
@@ -100,7 +109,7 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
     for (int i = 0; i < 4; ++i) acc[c][i][0] = acc[c][i][1] = acc[c][i][2] = acc[c][i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // rows g and g + 8
 
-  if (hi >= lo) {
+  if (hi >= lo || f_hi >= 0) {
     // Q fragments: row g and g + 8, 8 consecutive dims at 32c + 8 tq
     uint4 q_lo[DCH], q_hi[DCH];
     const bf16* qrow = q + (size_t)t * q_row_stride + (size_t)head0 * D;
@@ -118,7 +127,12 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
     const bf16* vbase = (const bf16*)cache.v;
 
     const int u_first = lo / kUnit, u_last = hi / kUnit;
-    for (int u = u_first + warp; u <= u_last; u += kDecWarps) {
+    const int n_kept = (f_hi + kUnit) / kUnit;           // units of kept first keys (f_hi = -1: none)
+    const int n_units = n_kept + (hi >= lo ? u_last - u_first + 1 : 0);
+    for (int x = warp; x < n_units; x += kDecWarps) {
+      const bool kept = x < n_kept;
+      const int u = kept ? x : u_first + (x - n_kept);
+      const int m_lo = kept ? 0 : lo, m_hi = kept ? f_hi : hi;     // the keys this visit may count
       const int key0 = u * kUnit;
       const int page = table[key0 / EK_PAGE];
       const size_t row0 = ((size_t)page * cache.heads + kv_head) * EK_PAGE + (key0 & (EK_PAGE - 1));
@@ -153,7 +167,7 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int key = key0 + 8 * j + 2 * tq + (e & 1);
-          const float v = (key >= lo && key <= hi) ? s[j][e] * scale_log2 : -INFINITY;
+          const float v = (key >= m_lo && key <= m_hi) ? s[j][e] * scale_log2 : -INFINITY;
           s[j][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
@@ -236,7 +250,9 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
       // a sink: one more term exp(sink) in the denominator, with no value (-inf: none)
       const float sk = sinks ? sinks[head] * 1.4426950408889634f : sink_log2;   // per head, if given
       if (sk > -INFINITY && l > 0.f) l += exp2f(sk - m);
-      out[((size_t)t * n_q_heads + head) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+      float res = l > 0.f ? o / l : 0.f;
+      if (gate != nullptr) res *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + head])));
+      out[((size_t)t * n_q_heads + head) * D + d] = __float2bfloat16_rn(res);
     } else {
       const size_t pi = ((size_t)t * n_q_heads + head) * n_splits + split;
       part_acc[pi * D + d] = o;
@@ -253,7 +269,8 @@ __global__ void attention_decode_combine_kernel(bf16* __restrict__ out,
                                                 const float* part_acc,
                                                 const float* part_ml, int n_q_heads,
                                                 int head_dim, int n_splits, float sink_log2,
-                                                const float* __restrict__ sinks) {
+                                                const float* __restrict__ sinks,
+                                                const bf16* __restrict__ gate, int gate_stride) {
   if (sinks != nullptr) sink_log2 = sinks[blockIdx.y] * 1.4426950408889634f;
   pdl_launch_dependents();
   pdl_wait();
@@ -265,7 +282,9 @@ __global__ void attention_decode_combine_kernel(bf16* __restrict__ out,
   for (int s = 0; s < n_splits; ++s)
     if (ml[2 * s + 1] > 0.f) l += ml[2 * s + 1] * exp2f(ml[2 * s] - m);
   if (sink_log2 > -INFINITY && l > 0.f) l += exp2f(sink_log2 - m);      // the sink, counted once
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  float inv = l > 0.f ? 1.f / l : 0.f;
+  if (gate != nullptr)
+    inv *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)blockIdx.x * gate_stride + blockIdx.y])));
   for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < n_splits; ++s)
@@ -279,7 +298,8 @@ template <int DCH>
 static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* positions,
                       const int* token_slot, PagedKV cache, int n_tokens, int n_q_heads,
                       float scale, int window, int n_splits, int keys_per_split, float* part_acc,
-                      float* part_ml, float sink, const float* sinks, cudaStream_t stream) {
+                      float* part_ml, float sink, const float* sinks, int keep_first, const bf16* gate,
+                      int gate_stride, cudaStream_t stream) {
   constexpr int D = DCH * 32;
   const int group = n_q_heads / cache.heads;
   const int row_blocks = (group + 15) / 16;
@@ -298,12 +318,13 @@ static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* pos
   cudaError_t e = launch_pdl(attention_decode_bf16_kernel<DCH>, grid, dim3(kDecWarps * 32), smem,
                              stream, out, q, q_row_stride, positions, token_slot, cache, n_q_heads,
                              row_blocks, scale * 1.4426950408889634f, window, n_splits,
-                             keys_per_split, part_acc, part_ml, sink * 1.4426950408889634f, sinks);
+                             keys_per_split, part_acc, part_ml, sink * 1.4426950408889634f, sinks,
+                             window > 0 ? keep_first : 0, gate, gate_stride);
   if (e != cudaSuccess || n_splits == 1) return (int)e;
   dim3 cgrid(n_tokens, n_q_heads);
   return (int)launch_pdl(attention_decode_combine_kernel, cgrid, dim3(64), 0, stream, out,
                          (const float*)part_acc, (const float*)part_ml, n_q_heads, D, n_splits,
-                         sink * 1.4426950408889634f, sinks);
+                         sink * 1.4426950408889634f, sinks, gate, gate_stride);
 }
 
 }  // namespace ek
@@ -318,7 +339,8 @@ EK_EXPORT int ek_attention_decode_bf16(void* out, const void* q, int q_row_strid
                                        int n_q_heads, int n_kv_heads, int head_dim, float scale,
                                        int window, int n_splits, int keys_per_split,
                                        float* part_acc, float* part_ml, float sink,
-                                       const float* sinks, cudaStream_t stream) {
+                                       const float* sinks, int keep_first, const void* gate,
+                                       int gate_stride, cudaStream_t stream) {
   using namespace ek;
   if (n_tokens <= 0) return 0;
   if (head_dim % 32 || head_dim < 32 || head_dim > 256 || n_kv_heads <= 0 ||
@@ -330,7 +352,7 @@ EK_EXPORT int ek_attention_decode_bf16(void* out, const void* q, int q_row_strid
   case DCH:                                                                                       \
     return launch_dch<DCH>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot, cache, \
                            n_tokens, n_q_heads, scale, window, n_splits, keys_per_split, part_acc, \
-                           part_ml, sink, sinks, stream);
+                           part_ml, sink, sinks, keep_first, (const bf16*)gate, gate_stride, stream);
   switch (head_dim / 32) {
     EK_CASE(1) EK_CASE(2) EK_CASE(3) EK_CASE(4) EK_CASE(5) EK_CASE(6) EK_CASE(7) EK_CASE(8)
   }
@@ -402,5 +424,5 @@ EK_EXPORT int ek_attention_decode_bf16_noalloc(void* out, const void* q, int q_r
   return ek_attention_decode_bf16(out, q, q_row_stride, positions, token_slot, k_pages, v_pages,
                                   block_table, table_stride, n_tokens, n_q_heads, n_kv_heads,
                                   head_dim, scale, window, n_splits, keys_per_split, part_acc,
-                                  part_ml, -INFINITY, nullptr, stream);
+                                  part_ml, -INFINITY, nullptr, 0, nullptr, 0, stream);
 }

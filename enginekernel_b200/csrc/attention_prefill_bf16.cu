@@ -10,6 +10,10 @@
 //     tokens, so a prompt cut into pieces, or appended to an earlier part, is the same
 //     code: a row at position p sees keys [max(0, p - window + 1), p];
 //   * one cache page (64 keys) is one key tile; K and V tiles are double-buffered.
+// `keep_first` > 0 (with a window): the first keep_first positions of the sequence stay visible to every
+// later row, beside its window - the tiles that hold them are walked before the window's.  `gate`, if
+// given, holds one value per token and query head (row stride `gate_stride`): the head's output is
+// multiplied by its sigmoid.
 // Tiles are found from cu_seqlens on the device (no host-built schedule).
 // The reference's counterpart is a Triton kernel over a padded rectangle, 128x128 tiles,
 // probabilities rounded to bfloat16 before P.V as here (engine/ek_kernels.py:166-221),
@@ -59,7 +63,8 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
                               const int* __restrict__ positions, const int* __restrict__ token_slot,
                               const int* __restrict__ cu_seqlens, int n_seqs, PagedKV cache,
                               int n_q_heads, float scale_log2, int window, int tok_per_tile,
-                              float sink_log2, const float* __restrict__ sinks) {
+                              float sink_log2, const float* __restrict__ sinks, int keep_first,
+                              const bf16* __restrict__ gate, int gate_stride) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int tile_info[3];                 // first token (packed index), tokens, sequence
   const int D = cache.head_dim;
@@ -106,6 +111,9 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   const int hi_tile = pos0 + n_tok - 1;
   const int lo_tile = window > 0 ? max(0, pos0 - window + 1) : 0;
   const int kt_lo = lo_tile / kPfKeys, kt_hi = hi_tile / kPfKeys;
+  // tiles of kept first keys that the window's tiles do not cover: 0 .. n_first - 1
+  const int n_first = keep_first > 0 ? min((keep_first + kPfKeys - 1) / kPfKeys, kt_lo) : 0;
+  const int n_tiles = n_first + kt_hi - kt_lo + 1;
   const int chunks = D / 8;                    // 16-byte pieces per row
 
   // ---- stage Q (rows beyond the real ones are zero) and the first K/V tile ---------------
@@ -133,7 +141,8 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
       cp_async16(vd + r * LD + c * 8, vsrc + (size_t)r * D + c * 8);
     }
   };
-  load_kv(kt_lo, 0);
+  auto tile_of = [&](int i) { return i < n_first ? i : kt_lo + (i - n_first); };
+  load_kv(tile_of(0), 0);
   cp_async_commit();
 
   // ---- per-thread state --------------------------------------------------------------------
@@ -148,9 +157,10 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   const int warp_pos_max = pos0 + min((warp * 16 + 15) / group, n_tok - 1);
   const bool warp_active = warp * 16 < n_rows;
 
-  for (int kt = kt_lo; kt <= kt_hi; ++kt) {
-    const int buf = (kt - kt_lo) & 1;
-    if (kt + 1 <= kt_hi) load_kv(kt + 1, buf ^ 1);
+  for (int it = 0; it < n_tiles; ++it) {
+    const int kt = tile_of(it);
+    const int buf = it & 1;
+    if (it + 1 < n_tiles) load_kv(tile_of(it + 1), buf ^ 1);
     cp_async_commit();
     cp_async_wait<1>();                        // tile kt (and Q) have landed
     __syncthreads();
@@ -158,7 +168,7 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     const int key0 = kt * kPfKeys;
     // a warp skips tiles none of its rows can see
     const bool tile_visible = warp_active && key0 <= warp_pos_max &&
-                              (window <= 0 || key0 + kPfKeys - 1 > warp_pos_min - window);
+                              (window <= 0 || key0 + kPfKeys - 1 > warp_pos_min - window || key0 < keep_first);
     if (tile_visible) {
       const bf16* kb = k_s + buf * kPfKeys * LD;
       const bf16* vb = v_s + buf * kPfKeys * LD;
@@ -193,7 +203,7 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
           if (need_mask) {
             const int key = key0 + 8 * j + 2 * tq + (e & 1);
             const int p = e < 2 ? pos_lo : pos_hi;
-            if (key > p || (window > 0 && key <= p - window)) v = -INFINITY;
+            if (key > p || (window > 0 && key <= p - window && key >= keep_first)) v = -INFINITY;
           }
           s[j][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -269,8 +279,16 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     for (int r = 0; r < 2; ++r)
       if (l_run[r] > 0.f) l_run[r] += exp2f(sink_log2 - m_run[r]);
   }
-  const float inv_lo = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
-  const float inv_hi = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+  float inv_lo = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
+  float inv_hi = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+  if (gate != nullptr) {
+    if (row_lo < n_rows)
+      inv_lo *= 1.f / (1.f + expf(-__bfloat162float(
+          gate[(size_t)(t_first + row_lo / group) * gate_stride + kv_head * group + row_lo % group])));
+    if (row_hi < n_rows)
+      inv_hi *= 1.f / (1.f + expf(-__bfloat162float(
+          gate[(size_t)(t_first + row_hi / group) * gate_stride + kv_head * group + row_hi % group])));
+  }
 #pragma unroll
   for (int i = 0; i < DMAX / 8; ++i) {
     const int d = 8 * i + 2 * tq;
@@ -293,7 +311,8 @@ template <int DMAX>
 static int launch_dmax(bf16* out, const bf16* q, int q_row_stride, const int* positions,
                        const int* token_slot, const int* cu_seqlens, int n_seqs, int n_tokens,
                        PagedKV cache, int n_q_heads, float scale, int window, float sink,
-                       const float* sinks, cudaStream_t stream) {
+                       const float* sinks, int keep_first, const bf16* gate, int gate_stride,
+                       cudaStream_t stream) {
   const int group = n_q_heads / cache.heads;
   const int tok_per_tile = kPfRows / group;
   const int D = cache.head_dim, LD = D + 8;
@@ -307,7 +326,8 @@ static int launch_dmax(bf16* out, const bf16* q, int q_row_stride, const int* po
   if (tiles > 65535) return EK_ERR_ARG;
   attention_prefill_bf16_kernel<DMAX><<<grid, kPfWarps * 32, smem, stream>>>(
       out, q, q_row_stride, positions, token_slot, cu_seqlens, n_seqs, cache, n_q_heads,
-      scale * 1.4426950408889634f, window, tok_per_tile, sink * 1.4426950408889634f, sinks);
+      scale * 1.4426950408889634f, window, tok_per_tile, sink * 1.4426950408889634f, sinks,
+      window > 0 ? keep_first : 0, gate, gate_stride);
   EK_RETURN_LAUNCH_STATUS();
 }
 
@@ -324,7 +344,8 @@ EK_EXPORT int ek_attention_prefill_bf16(void* out, const void* q, int q_row_stri
                                         const void* k_pages, const void* v_pages,
                                         const int* block_table, int table_stride, int n_q_heads,
                                         int n_kv_heads, int head_dim, float scale, int window,
-                                        float sink, const float* sinks, cudaStream_t stream) {
+                                        float sink, const float* sinks, int keep_first,
+                                        const void* gate, int gate_stride, cudaStream_t stream) {
   using namespace ek;
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if (head_dim % 16 || head_dim < 16 || head_dim > 256 || n_kv_heads <= 0 ||
@@ -333,10 +354,13 @@ EK_EXPORT int ek_attention_prefill_bf16(void* out, const void* q, int q_row_stri
   PagedKV cache{(void*)k_pages, (void*)v_pages, block_table, table_stride, n_kv_heads, head_dim};
   if (head_dim <= 64)
     return launch_dmax<64>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot,
-                           cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, sinks, stream);
+                           cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, sinks,
+                           keep_first, (const bf16*)gate, gate_stride, stream);
   if (head_dim <= 128)
     return launch_dmax<128>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot,
-                            cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, sinks, stream);
+                            cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, sinks,
+                           keep_first, (const bf16*)gate, gate_stride, stream);
   return launch_dmax<256>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot,
-                          cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, sinks, stream);
+                          cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, sinks,
+                           keep_first, (const bf16*)gate, gate_stride, stream);
 }

@@ -399,7 +399,15 @@ def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages,
 
 _attn_decode_bf16 = Function("attention_decode_bf16", "ek_attention_decode_bf16",
                              [_P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
-                              c_float, c_int, c_int, c_int, _P, _P, c_float, _P, _P])
+                              c_float, c_int, c_int, c_int, _P, _P, c_float, _P, c_int, _P, c_int, _P])
+
+
+def _gate_args(gate, q, n_q_heads):
+    """(pointer, row stride) of the optional per-head gate, checked."""
+    _need(gate is None or (gate.is_cuda and gate.dtype == q.dtype and gate.stride(-1) == 1
+                           and gate.shape[-1] >= n_q_heads),
+          "attention: the gate holds one value per token and query head, in q's dtype")
+    return _ptr(gate), (gate.stride(0) if gate is not None else 0)
 
 
 def attention_decode_supported(dtype, head_dim):
@@ -408,10 +416,11 @@ def attention_decode_supported(dtype, head_dim):
 
 def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table,
                           n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1,
-                          keys_per_split=0, part_acc=None, part_ml=None, sink=None, sinks=None):
+                          keys_per_split=0, part_acc=None, part_ml=None, sink=None, sinks=None, keep_first=0,
+                          gate=None):
     """One query token per row of ``q`` (bfloat16, head_dim a multiple of 32): same contract
-    as :func:`attention_generic`; ``keys_per_split`` must be a multiple of 16, or 0 to cut
-    every token's own visible keys into ``n_splits`` equal parts."""
+    as :func:`attention_generic` (``keep_first`` and ``gate`` included); ``keys_per_split`` must be a
+    multiple of 16, or 0 to cut every token's own window into ``n_splits`` equal parts."""
     _need_cuda(out, q, positions, token_slot, k_pages, v_pages, block_table, part_acc, part_ml)
     _need(attention_decode_supported(q.dtype, head_dim),
           "attention_decode_bf16: bfloat16 and a head size that is a multiple of 32")
@@ -428,7 +437,7 @@ def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pa
                       _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
                       n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
                       n_splits, keys_per_split, _ptr(part_acc), _ptr(part_ml), _sink(sink),
-                      _sinks(sinks, n_q_heads), _stream())
+                      _sinks(sinks, n_q_heads), int(keep_first or 0), *_gate_args(gate, q, n_q_heads), _stream())
     if n_splits > 1:
         count_extra_launches()               # the merge kernel
 
@@ -489,7 +498,7 @@ def attention_decode_tma(out, q, n_tokens, positions, token_slot, k_pages, v_pag
 
 _attn_prefill_bf16 = Function("attention_prefill_bf16", "ek_attention_prefill_bf16",
                               [_P, _P, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, c_int,
-                               c_int, c_int, c_float, c_int, c_float, _P, _P])
+                               c_int, c_int, c_float, c_int, c_float, _P, c_int, _P, c_int, _P])
 
 
 def attention_prefill_supported(dtype, head_dim, n_q_heads, n_kv_heads):
@@ -499,10 +508,10 @@ def attention_prefill_supported(dtype, head_dim, n_q_heads, n_kv_heads):
 
 def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, n_seqs, k_pages,
                            v_pages, block_table, n_q_heads, n_kv_heads, head_dim, scale,
-                           window=None, sink=None, sinks=None):
+                           window=None, sink=None, sinks=None, keep_first=0, gate=None):
     """Several new tokens per sequence (bfloat16): sequence b owns rows cu_seqlens[b] ..
     cu_seqlens[b+1] of ``q``, which stand at consecutive positions; their keys and values
-    are already in the pages."""
+    are already in the pages.  ``keep_first`` and ``gate`` as in :func:`attention_generic`."""
     _need_cuda(out, q, positions, token_slot, cu_seqlens, k_pages, v_pages, block_table)
     _need(attention_prefill_supported(q.dtype, head_dim, n_q_heads, n_kv_heads),
           "attention_prefill_bf16: bfloat16, head size a multiple of 16, at most 128 heads a group")
@@ -514,7 +523,8 @@ def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, 
     _attn_prefill_bf16(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                        _ptr(cu_seqlens), n_seqs, n_tokens, _ptr(k_pages), _ptr(v_pages),
                        _ptr(block_table), block_table.stride(0), n_q_heads, n_kv_heads, head_dim,
-                       float(scale), int(window or 0), _sink(sink), _sinks(sinks, n_q_heads), _stream())
+                       float(scale), int(window or 0), _sink(sink), _sinks(sinks, n_q_heads),
+                       int(keep_first or 0), *_gate_args(gate, q, n_q_heads), _stream())
 
 
 _attn_prefill_tc = Function("attention_prefill_tc", "ek_attention_prefill_tc",

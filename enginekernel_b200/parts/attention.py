@@ -115,7 +115,11 @@ class Attention(Mixer):
                                  "temperature, the gained q/k norm or a sink")
             if self.keep_first and not self.window:
                 raise ValueError("attention: keep_first needs a window")
-            self.padded_dim = -(-max(self.head_dim, self.value_dim) // 8) * 8
+            # (a multiple of 32 where the 16-bit attention kernels can take it: at most a quarter more)
+            widest = max(self.head_dim, self.value_dim)
+            self.padded_dim = -(-widest // 32) * 32 if dtype == torch.bfloat16 and widest >= 64 else -(-widest // 8) * 8
+            if self.padded_dim > kernels.MAX_HEAD_DIM:
+                self.padded_dim = -(-widest // 8) * 8
             kernels.check_head_dim(self.padded_dim)
             # (this path takes normalised activations and returns a plain tensor)
             self.takes_deferred_norm = self.defers_norm = False
@@ -194,6 +198,25 @@ class Attention(Mixer):
             write_kv=writes_cache and self.kv_projection)
         out = ctx.workspace.get("attn_out", (t, nh * big), self.dtype)
         visible = min(ctx.max_context, self.window + self.keep_first) if self.window else ctx.max_context
+        gate = rows[:, gate_col:] if self.head_gate else None
+        if not ctx.is_decode and kernels.attention_prefill_supported(self.dtype, big, nh, nkv):
+            kernels.attention_prefill_bf16(out, rows, t, ctx.positions, ctx.token_slot, ctx.cu_seqlens, ctx.n_seqs,
+                                           entry.k_pages, entry.v_pages, entry.block_table, nh, nkv, big, self.scale,
+                                           self.window, keep_first=self.keep_first, gate=gate)
+            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t)
+        if ctx.is_decode and kernels.attention_decode_supported(self.dtype, big):
+            # blocks = tokens x KV heads (x 16-row blocks of the group), three fit an SM: every token's own
+            # window is cut so that the blocks about fill the machine, never finer than two pages a split
+            blocks = t * nkv * -(-(nh // nkv) // 16)
+            splits = max(1, min(3 * kernels.sm_count(self.device) // blocks, -(-visible // 128)))
+            acc = ml = None
+            if splits > 1:
+                acc = ctx.workspace.get("attn_part_acc", (t, nh, splits, big), torch.float32)
+                ml = ctx.workspace.get("attn_part_ml", (t, nh, splits, 2), torch.float32)
+            kernels.attention_decode_bf16(out, rows, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
+                                          entry.block_table, nh, nkv, big, self.scale, self.window, splits, 0, acc, ml,
+                                          keep_first=self.keep_first, gate=gate)
+            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t)
         splits, per_split, acc, ml = 1, 0, None, None
         blocks = t * nh
         if blocks < 2 * kernels.sm_count(self.device) and visible > 512:
@@ -206,8 +229,7 @@ class Attention(Mixer):
             ml = ctx.workspace.get("attn_part_ml", (t, nh, splits, 2), torch.float32)
         kernels.attention_generic(out, rows, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
                                   entry.block_table, nh, nkv, big, self.scale, self.window, splits, per_split,
-                                  acc, ml, keep_first=self.keep_first,
-                                  gate=rows[:, gate_col:] if self.head_gate else None)
+                                  acc, ml, keep_first=self.keep_first, gate=gate)
         return linear(out, self.w_o, ctx, "attn_proj", n_rows=t)
 
     def load(self, tensors):

@@ -151,6 +151,63 @@ def test_window_with_kept_first_tokens_and_head_gate(dtype, window, keep, length
         assert hit == seen, (j, seen)
 
 
+@pytest.mark.parametrize("d,nq,nkv", [(64, 4, 2), (96, 6, 1), (128, 8, 8)])
+@pytest.mark.parametrize("window,keep,length", [(9, 3, 40), (70, 5, 300), (64, 64, 200), (3, 1, 700), (130, 70, 400)])
+def test_the_16_bit_prompt_and_decode_kernels_keep_first_tokens_and_gate(d, nq, nkv, window, keep, length):
+    """The same rule in the two fast bfloat16 kernels: a whole prompt, a portion of two sequences' tokens behind
+    what the cache already holds, single tokens with the window cut into several splits, and the one key that
+    stands out at every edge."""
+    k = K()
+    dtype, scale = torch.bfloat16, 0.2
+    pages = Pages(2, length, nkv, d, dtype, seed=window + d)
+    keys, values = rnd(length, nkv, d, dtype=dtype, seed=1), rnd(length, nkv, d, dtype=dtype, seed=2)
+    pages.fill(0, keys, values)
+    pages.fill(1, keys, values)
+    q = rnd(length, nq * d + 8, dtype=dtype, seed=3)
+    gate = q[:, nq * d:]
+    kc, vc, qc = keys.cpu(), values.cpu(), q.cpu()
+    want = lambda pos: _window_reference(qc[pos, :nq * d].view(nq, d), kc, vc, pos, scale, window, keep, qc[pos, nq * d:])
+    out = torch.empty(length, nq * d, dtype=dtype, device=DEV)
+    k.attention_prefill_bf16(out, q, length, i32(list(range(length))), i32([0] * length), i32([0, length]), 1, pages.k,
+                             pages.v, pages.table, nq, nkv, d, scale, window, keep_first=keep, gate=gate)
+    edges = sorted({0, 1, keep, keep + 1, window - 1, window, window + keep, 63, 64, 65, 127, 128, length - 1} & set(range(length)))
+    for pos in edges:
+        assert rel(out[pos], want(pos)) <= 2e-2, pos
+    # the last 5 tokens of slot 0 and the last 2 of slot 1 as one step
+    rows = torch.cat([q[length - 5:], q[length - 2:]]).contiguous()
+    pos = list(range(length - 5, length)) + [length - 2, length - 1]
+    o2 = torch.empty(7, nq * d, dtype=dtype, device=DEV)
+    k.attention_prefill_bf16(o2, rows, 7, i32(pos), i32([0] * 5 + [1] * 2), i32([0, 5, 7]), 2, pages.k, pages.v,
+                             pages.table, nq, nkv, d, scale, window, keep_first=keep, gate=rows[:, nq * d:])
+    assert rel(o2, torch.cat([out[length - 5:], out[length - 2:]])) <= 2e-2
+    for splits in (1, 3):
+        acc = torch.empty(len(edges), nq, splits, d, device=DEV)
+        ml = torch.empty(len(edges), nq, splits, 2, device=DEV)
+        rows = q[edges].contiguous()
+        o3 = torch.empty(len(edges), nq * d, dtype=dtype, device=DEV)
+        k.attention_decode_bf16(o3, rows, len(edges), i32(edges), i32([1] * len(edges)), pages.k, pages.v, pages.table,
+                                nq, nkv, d, scale, window, splits, 0, acc, ml, keep_first=keep, gate=rows[:, nq * d:])
+        for r, pos in enumerate(edges):
+            assert rel(o3[r], want(pos)) <= 2e-2, (splits, pos)
+    last = length - 1
+    sharp_q = torch.zeros(2, nq * d, dtype=dtype, device=DEV)
+    sharp_q.view(2, nq, d)[:, :, 0] = 30.0
+    o1 = torch.empty(2, nq * d, dtype=dtype, device=DEV)
+    acc, ml = torch.empty(1, nq, 2, d, device=DEV), torch.empty(1, nq, 2, 2, device=DEV)
+    for j in sorted({0, keep - 1, keep, last - window, last - window + 1, 63, 64, last} & set(range(length))):
+        k2 = (keys.float() * 0.1).to(dtype)
+        k2[j, :, 0] = 30.0
+        pages.fill(0, k2, values)
+        seen = plain.visible(last, j, window, keep)
+        hit = lambda o: rel(o.view(nq, d), vc[j].repeat_interleave(nq // nkv, 0)) <= 2e-2
+        k.attention_prefill_bf16(o1, sharp_q, 2, i32([last - 1, last]), i32([0, 0]), i32([0, 2]), 1, pages.k, pages.v,
+                                 pages.table, nq, nkv, d, scale, window, keep_first=keep)
+        assert hit(o1[1]) == seen, ("prompt", j, seen)
+        k.attention_decode_bf16(o1[:1], sharp_q[:1], 1, i32([last]), i32([0]), pages.k, pages.v, pages.table, nq, nkv, d,
+                                scale, window, 2, 0, acc, ml, keep_first=keep)
+        assert hit(o1[0]) == seen, ("decode", j, seen)
+
+
 @pytest.mark.parametrize("channels,taps", [(30, 4), (7, 1), (300, 2), (64, 5)])
 def test_convolution_with_carried_inputs(channels, taps):
     """A sequence run whole, and cut 1 + 2 + 8 + rest behind another sequence's tokens (portions shorter than the
