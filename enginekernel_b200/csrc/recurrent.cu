@@ -36,32 +36,42 @@ __device__ __forceinline__ int step_predecessors(const int* positions, const int
   return n;
 }
 
-// grid: tokens.  out[t, c] = silu(bias[c] + sum_j w[c][K-1-j] x[t-j, c]) with x = proj[., col0 + c].
-// tail of a slot: [channels][K-1], oldest first.
+// grid (token tiles, channel tiles).  out[t, c] = silu(bias[c] + sum_j w[c][K-1-j] x[t-j, c]) with
+// x = proj[., col0 + c].  tail of a slot: [channels][K-1], oldest first.  A block takes `per_block`
+// neighbouring tokens (at most 16), so that a prompt's rows are fetched once into L1 for all their taps.
+constexpr int kConvTokens = 16;
 __global__ void __launch_bounds__(256)
 conv_silu_kernel(float* __restrict__ out, int out_stride, const float* __restrict__ proj, int proj_stride, int col0,
                  const float* __restrict__ conv_w, const float* __restrict__ conv_b,
                  const float* __restrict__ state, size_t slot_stride, size_t tail_offset,
-                 const int* __restrict__ positions, const int* __restrict__ token_slot, int channels, int K) {
-  __shared__ int n_prev_s;
+                 const int* __restrict__ positions, const int* __restrict__ token_slot, int n_tokens, int channels,
+                 int K, int per_block) {
+  __shared__ int n_prev_s[kConvTokens], slot_s[kConvTokens];
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
-  if (positions[t] < 0) return;
-  if (threadIdx.x == 0) n_prev_s = step_predecessors(positions, token_slot, t, K - 1);
+  const int t0 = blockIdx.x * per_block, nt = min(per_block, n_tokens - t0);
+  if ((int)threadIdx.x < nt) {
+    const int t = t0 + threadIdx.x;
+    const bool live = positions[t] >= 0;
+    n_prev_s[threadIdx.x] = live ? step_predecessors(positions, token_slot, t, K - 1) : -1;
+    slot_s[threadIdx.x] = live ? token_slot[t] : 0;
+  }
   __syncthreads();
-  const int n_prev = n_prev_s;
-  const float* tail = state + (size_t)token_slot[t] * slot_stride + tail_offset;
-  const float* row = proj + (size_t)t * proj_stride + col0;
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
     const float* w = conv_w + (size_t)c * K;
-    float acc = (conv_b ? conv_b[c] : 0.f) + w[K - 1] * row[c];
-    for (int j = 1; j < K; ++j) {
-      const float x = j <= n_prev ? proj[(size_t)(t - j) * proj_stride + col0 + c]
-                                  : tail[(size_t)c * (K - 1) + (n_prev - j + K - 1)];
-      acc = fmaf(w[K - 1 - j], x, acc);
+    const float bias = conv_b ? conv_b[c] : 0.f;
+    for (int i = 0; i < nt; ++i) {
+      const int n_prev = n_prev_s[i], t = t0 + i;
+      if (n_prev < 0) continue;
+      const float* tail = state + (size_t)slot_s[i] * slot_stride + tail_offset;
+      float acc = bias + w[K - 1] * proj[(size_t)t * proj_stride + col0 + c];
+      for (int j = 1; j < K; ++j) {
+        const float x = j <= n_prev ? proj[(size_t)(t - j) * proj_stride + col0 + c]
+                                    : tail[(size_t)c * (K - 1) + (n_prev - j + K - 1)];
+        acc = fmaf(w[K - 1 - j], x, acc);
+      }
+      out[(size_t)t * out_stride + c] = acc * sigmoid_f(acc);
     }
-    out[(size_t)t * out_stride + c] = acc * sigmoid_f(acc);
   }
 }
 
@@ -122,14 +132,26 @@ xgate_scan_kernel(float* __restrict__ a, float* __restrict__ b, float* __restric
   float* m_state = state + (size_t)token_slot[start] * slot_stride + m_offset + h;
   float m_in = *m_state;
   const float bi = bias_i[h], bf = bias_f[h];
+  // raw gate inputs of the next 32 tokens are fetched while this pass runs
+  auto raw = [&](int c0, float& xi, float& xf) {
+    xi = xf = 0.f;
+    if (c0 + lane < n) {
+      const float* row = proj + (size_t)(start + c0 + lane) * proj_stride;
+      xi = row[col_i + h];
+      xf = row[col_f + h];
+    }
+  };
+  float xi_next, xf_next;
+  raw(0, xi_next, xf_next);
   for (int c0 = 0; c0 < n; c0 += 32) {
     const int t = start + c0 + lane;
     const bool live = c0 + lane < n;
+    const float xi = xi_next, xf = xf_next;
+    if (c0 + 32 < n) raw(c0 + 32, xi_next, xf_next);
     float gi = 0.f, gf = 0.f;                    // the identity map for lanes past the end: F = 0, I = -inf
     if (live) {
-      const float* row = proj + (size_t)t * proj_stride;
-      gi = cap * tanhf((row[col_i + h] + bi) / cap);
-      gf = -softplus_f(-(cap * tanhf((row[col_f + h] + bf) / cap)));
+      gi = cap * tanhf((xi + bi) / cap);
+      gf = -softplus_f(-(cap * tanhf((xf + bf) / cap)));
     }
     float F = live ? gf : 0.f, I = live ? gi : -INFINITY;
 #pragma unroll
@@ -152,13 +174,15 @@ xgate_scan_kernel(float* __restrict__ a, float* __restrict__ b, float* __restric
 
 constexpr int kScanCols = 16;        // columns of S a block takes
 constexpr int kScanLanes = 8;        // lanes that share a column
-constexpr int kScanChunk = 16;       // tokens fetched into shared memory at a time
 constexpr int kScanThreads = kScanCols * kScanLanes;
+constexpr int kScanFloats = 2048;    // values of keys (and of queries) fetched into shared memory at a time
 
 // grid (sequences, heads, column tiles).  RPL rows of a column a lane: lane l holds rows 32 g + 4 l + c
 // (g < RPL / 4, c < 4), so that the 8 lanes of a column read 128 neighbouring bytes of a key at a time.
 // S of a slot: state[((h * C + j) * DK + i], DK = 8 RPL rows (keys padded with zeros), C = dv + ones_col columns.
 // Column dv (with ones_col) has v = 1: it carries n_t = a n + b k and gives n.q.
+// Tokens come 2048 / DK at a time: while one portion is worked through from shared memory, the next one's
+// keys, queries, values and gates are already on their way into registers.
 template <int RPL>
 __global__ void __launch_bounds__(kScanThreads)
 decay_scan_kernel(float* __restrict__ out, int out_stride, const float* __restrict__ q, int q_stride,
@@ -167,11 +191,15 @@ decay_scan_kernel(float* __restrict__ out, int out_stride, const float* __restri
                   size_t slot_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
                   const int* __restrict__ token_slot, int heads, int kv_heads, int dk, int dv, int ones_col,
                   int write_state) {
-  constexpr int DK = 8 * RPL, G4 = RPL / 4;
-  __shared__ __align__(16) float k_s[kScanChunk][DK];
-  __shared__ __align__(16) float q_s[kScanChunk][DK];
-  __shared__ float v_s[kScanChunk][kScanCols];
-  __shared__ float a_s[kScanChunk], b_s[kScanChunk];
+  constexpr int DK = 8 * RPL, G4 = RPL / 4, DK4 = DK / 4;
+  constexpr int CH = kScanFloats / DK;                       // tokens a portion: 64, 32, 16 or 8
+  constexpr int NV4 = kScanFloats / 4 / kScanThreads;        // float4 of keys (of queries) a thread fetches
+  constexpr int NV = CH * kScanCols / kScanThreads;          // values a thread fetches
+  static_assert(CH <= kScanThreads && CH * kScanCols % kScanThreads == 0, "portion sizes");
+  __shared__ __align__(16) float k_s[CH][DK];
+  __shared__ __align__(16) float q_s[CH][DK];
+  __shared__ float v_s[CH][kScanCols];
+  __shared__ float a_s[CH], b_s[CH];
   pdl_launch_dependents();
   pdl_wait();
   const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kScanCols;
@@ -181,33 +209,71 @@ decay_scan_kernel(float* __restrict__ out, int out_stride, const float* __restri
   const int C = dv + ones_col, j = col0 + col;
   const bool live = j < C;
   const int kv = h / (heads / kv_heads);
+  // whole float4 loads need rows and head offsets on 16-byte boundaries
+  const bool vec = dk % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 &&
+                   (((uintptr_t)q | (uintptr_t)k) & 15) == 0;
   float* sp = state + (size_t)token_slot[start] * slot_stride + ((size_t)h * C + (live ? j : 0)) * DK;
   float4 S[G4];
 #pragma unroll
   for (int g = 0; g < G4; ++g)
     S[g] = live ? *reinterpret_cast<const float4*>(sp + 32 * g + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int c0 = 0; c0 < n; c0 += kScanChunk) {
-    const int nc = min(kScanChunk, n - c0);
-    __syncthreads();                             // the chunk before is worked through
-    for (int idx = tid; idx < nc * DK; idx += kScanThreads) {
-      const int tt = idx / DK, i = idx % DK;
-      const size_t t = start + c0 + tt;
-      k_s[tt][i] = i < dk ? k[t * k_stride + (size_t)kv * dk + i] : 0.f;
-      q_s[tt][i] = i < dk ? q[t * q_stride + (size_t)kv * dk + i] : 0.f;
+
+  float4 k_r[NV4], q_r[NV4];
+  float v_r[NV], a_r = 1.f, b_r = 0.f;
+  // rows past the portion's end, and keys past dk, stay zero: the loads are predicated, nothing is selected
+  // from a loaded value, so a fetch does not wait for what it asked for
+  auto row4 = [&](float4& r, const float* base, size_t t, int stride, int i) {
+    const float* p = base + t * stride + (size_t)kv * dk + i;
+    if (vec) {
+      if (i < dk) r = *reinterpret_cast<const float4*>(p);
+    } else {
+      if (i < dk) r.x = p[0];
+      if (i + 1 < dk) r.y = p[1];
+      if (i + 2 < dk) r.z = p[2];
+      if (i + 3 < dk) r.w = p[3];
     }
-    for (int idx = tid; idx < nc * kScanCols; idx += kScanThreads) {
-      const int tt = idx / kScanCols, cc = idx % kScanCols, jj = col0 + cc;
-      const size_t t = start + c0 + tt;
-      v_s[tt][cc] = jj < dv ? v[t * v_stride + (size_t)h * dv + jj] : (jj < C ? 1.f : 0.f);
+  };
+  auto fetch = [&](int c0) {
+    const int nc = min(CH, n - c0);
+#pragma unroll
+    for (int m = 0; m < NV4; ++m) {
+      const int f = tid + m * kScanThreads, tt = f / DK4, i = (f % DK4) * 4;
+      k_r[m] = q_r[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (tt < nc) {
+        row4(k_r[m], k, (size_t)start + c0 + tt, k_stride, i);
+        row4(q_r[m], q, (size_t)start + c0 + tt, q_stride, i);
+      }
     }
+#pragma unroll
+    for (int m = 0; m < NV; ++m) {
+      const int f = tid + m * kScanThreads, tt = f / kScanCols, jj = col0 + f % kScanCols;
+      v_r[m] = jj >= dv && jj < C ? 1.f : 0.f;
+      if (tt < nc && jj < dv) v_r[m] = v[((size_t)start + c0 + tt) * v_stride + (size_t)h * dv + jj];
+    }
+    a_r = 1.f, b_r = 0.f;                        // tokens past the end leave S as it is
     if (tid < nc) {
-      a_s[tid] = a[(size_t)(start + c0 + tid) * heads + h];
-      b_s[tid] = b[(size_t)(start + c0 + tid) * heads + h];
+      a_r = a[((size_t)start + c0 + tid) * heads + h];
+      b_r = b[((size_t)start + c0 + tid) * heads + h];
     }
+  };
+  fetch(0);
+  for (int c0 = 0; c0 < n; c0 += CH) {
+    const int nc = min(CH, n - c0);
+    __syncthreads();                             // the portion before is worked through
+#pragma unroll
+    for (int m = 0; m < NV4; ++m) {
+      const int f = tid + m * kScanThreads;
+      reinterpret_cast<float4*>(&k_s[0][0])[f] = k_r[m];
+      reinterpret_cast<float4*>(&q_s[0][0])[f] = q_r[m];
+    }
+#pragma unroll
+    for (int m = 0; m < NV; ++m) (&v_s[0][0])[tid + m * kScanThreads] = v_r[m];
+    if (tid < CH) { a_s[tid] = a_r; b_s[tid] = b_r; }
     __syncthreads();
-    for (int tt = 0; tt < nc; ++tt) {
+    if (c0 + CH < n) fetch(c0 + CH);
+    auto token = [&](int tt) {                   // S <- a S + b v k, returns this lane's part of S^T q
       const float aa = a_s[tt], bv = b_s[tt] * v_s[tt][col];
-      float acc = 0.f;
+      float acc[G4];
 #pragma unroll
       for (int g = 0; g < G4; ++g) {
         const float4 kk = *reinterpret_cast<const float4*>(&k_s[tt][32 * g + 4 * lane]);
@@ -216,15 +282,40 @@ decay_scan_kernel(float* __restrict__ out, int out_stride, const float* __restri
         S[g].y = fmaf(aa, S[g].y, bv * kk.y);
         S[g].z = fmaf(aa, S[g].z, bv * kk.z);
         S[g].w = fmaf(aa, S[g].w, bv * kk.w);
-        acc = fmaf(S[g].x, qq.x, acc);
-        acc = fmaf(S[g].y, qq.y, acc);
-        acc = fmaf(S[g].z, qq.z, acc);
-        acc = fmaf(S[g].w, qq.w, acc);
+        acc[g] = fmaf(S[g].w, qq.w, fmaf(S[g].z, qq.z, fmaf(S[g].y, qq.y, S[g].x * qq.x)));
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (lane == 0 && live) out[(size_t)(start + c0 + tt) * out_stride + (size_t)h * C + j] = acc;
+      float sum = acc[0];
+#pragma unroll
+      for (int g = 1; g < G4; ++g) sum += acc[g];
+      return sum;
+    };
+    int tt = 0;
+    // eight tokens at a time: their partial sums are exchanged so that lane l ends with token l's total
+    // (7 shuffles in 3 levels for 8 tokens instead of 24 in 24)
+    for (; tt + 8 <= nc; tt += 8) {
+      float p[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) p[u] = token(tt + u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float send = (lane & 4) ? p[u] : p[u + 4], keep = (lane & 4) ? p[u + 4] : p[u];
+        p[u] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const float send = (lane & 2) ? p[u] : p[u + 2], keep = (lane & 2) ? p[u + 2] : p[u];
+        p[u] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+      }
+      const float send = (lane & 1) ? p[0] : p[1], keep = (lane & 1) ? p[1] : p[0];
+      const float total = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+      if (live) out[(size_t)(start + c0 + tt + lane) * out_stride + (size_t)h * C + j] = total;
+    }
+    for (; tt < nc; ++tt) {
+      float sum = token(tt);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      if (lane == 0 && live) out[(size_t)(start + c0 + tt) * out_stride + (size_t)h * C + j] = sum;
     }
   }
   if (write_state && live) {
@@ -236,7 +327,7 @@ decay_scan_kernel(float* __restrict__ out, int out_stride, const float* __restri
 // grid (tokens, parts).  y[t, c] = rms-normed over the part ((o + D[h] x) silu(z)) * w[c]; o [T, inner] from
 // the scan, x [T, .] the convolved inputs (stride x_stride), z = proj[t, col_z + c]; a head is vdim channels.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 ssm_out_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __restrict__ x, int x_stride,
                const float* __restrict__ proj, int proj_stride, int col_z, const float* __restrict__ d_skip,
                const float* __restrict__ w, float eps, const int* __restrict__ positions, int inner, int vdim,
@@ -292,9 +383,12 @@ EK_EXPORT int ek_conv_silu(float* out, int out_stride, const float* proj, int pr
                            int channels, int taps, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (channels <= 0 || taps < 1) return EK_ERR_ARG;
-  return (int)ek::launch_pdl(ek::conv_silu_kernel, dim3(n_tokens), dim3(256), 0, stream, out, out_stride, proj,
-                             proj_stride, col0, conv_w, conv_b, state, (size_t)slot_stride, (size_t)tail_offset,
-                             positions, token_slot, channels, taps);
+  const int tiles = (channels + 255) / 256;
+  const int per_block = n_tokens >= 2048 ? ek::kConvTokens : n_tokens >= 256 ? 4 : 1;
+  return (int)ek::launch_pdl(ek::conv_silu_kernel, dim3((n_tokens + per_block - 1) / per_block, tiles < 65535 ? tiles : 65535),
+                             dim3(256), 0, stream, out, out_stride, proj, proj_stride, col0, conv_w, conv_b, state,
+                             (size_t)slot_stride, (size_t)tail_offset, positions, token_slot, n_tokens, channels,
+                             taps, per_block);
 }
 
 EK_EXPORT int ek_conv_tail(float* state, long long slot_stride, long long tail_offset, const float* proj,
@@ -361,9 +455,11 @@ EK_EXPORT int ek_decay_scan(float* out, int out_stride, const float* q, int q_st
     if (n_tokens <= 0) return 0;                                                                               \
     if (inner <= 0 || vdim <= 0 || parts <= 0 || inner % parts || inner % vdim || parts > 65535)               \
       return EK_ERR_ARG;                                                                                       \
-    return (int)ek::launch_pdl(ek::ssm_out_kernel<T>, dim3(n_tokens, parts), dim3(256), 0, stream, (T*)y, o, x, \
-                               x_stride, proj, proj_stride, col_z, d_skip, w, eps, positions, inner, vdim,     \
-                               parts);                                                                         \
+    const int size = inner / parts; /* a thread takes up to four channels of a part */                         \
+    const int threads = size >= 4096 ? 1024 : size <= 256 ? 64 : (size / 4 + 31) / 32 * 32;                    \
+    return (int)ek::launch_pdl(ek::ssm_out_kernel<T>, dim3(n_tokens, parts), dim3(threads), 0, stream, (T*)y,  \
+                               o, x, x_stride, proj, proj_stride, col_z, d_skip, w, eps, positions, inner,     \
+                               vdim, parts);                                                                   \
   }                                                                                                            \
   EK_EXPORT int ek_xlstm_out_##SUFFIX(void* y, const float* o, const float* m_run, const float* proj,          \
                                       int proj_stride, int col_g, const float* w, float eps, float q_scale,    \
