@@ -110,11 +110,12 @@ __global__ void ssm_gates_kernel(float* __restrict__ a, float* __restrict__ b, c
   b[idx] = dt;
 }
 
-// grid (sequences, heads / warps a block); a warp a head.  Log input gate i = cap tanh((x_i + b_i) / cap),
+// grid (sequences, heads); a block a head, 32 tokens a warp.  Log input gate i = cap tanh((x_i + b_i) / cap),
 // log forget gate f = logsigmoid(cap tanh((x_f + b_f) / cap)); m_t = max(f_t + m_(t-1), i_t) from the
-// state's m; a = exp(f + m_(t-1) - m_t), b = exp(i - m_t), m_run[t, h] = m_t.  The maximum over 32 tokens
-// at a time: the maps m -> max(m + F, I) compose as (F1 + F2, max(I1 + F2, I2)).
-constexpr int kGateWarps = 4;
+// state's m; a = exp(f + m_(t-1) - m_t), b = exp(i - m_t), m_run[t, h] = m_t.  The maximum is a scan: the
+// maps m -> max(m + F, I) compose as (F1 + F2, max(I1 + F2, I2)); a warp composes its 32 tokens by shuffles,
+// the warps' totals meet in shared memory, and 256 tokens are done a pass with no chain from token to token.
+constexpr int kGateWarps = 8;
 __global__ void __launch_bounds__(kGateWarps * 32)
 xgate_scan_kernel(float* __restrict__ a, float* __restrict__ b, float* __restrict__ m_run,
                   const float* __restrict__ proj, int proj_stride, int col_i, int col_f,
@@ -122,54 +123,61 @@ xgate_scan_kernel(float* __restrict__ a, float* __restrict__ b, float* __restric
                   float* __restrict__ state, size_t slot_stride, size_t m_offset,
                   const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
                   const int* __restrict__ token_slot, int heads, int write_state) {
+  __shared__ float F_s[2][kGateWarps], I_s[2][kGateWarps];
   pdl_launch_dependents();
   pdl_wait();
-  const int seq = blockIdx.x, lane = threadIdx.x & 31;
-  const int h = blockIdx.y * kGateWarps + (threadIdx.x >> 5);
-  if (h >= heads) return;
+  const int seq = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int start = cu_seqlens[seq], n = cu_seqlens[seq + 1] - start;
   if (n <= 0 || positions[start] < 0) return;
   float* m_state = state + (size_t)token_slot[start] * slot_stride + m_offset + h;
   float m_in = *m_state;
   const float bi = bias_i[h], bf = bias_f[h];
-  // raw gate inputs of the next 32 tokens are fetched while this pass runs
+  // raw gate inputs of the next pass are fetched while this one runs
   auto raw = [&](int c0, float& xi, float& xf) {
     xi = xf = 0.f;
-    if (c0 + lane < n) {
-      const float* row = proj + (size_t)(start + c0 + lane) * proj_stride;
+    if (c0 + (int)threadIdx.x < n) {
+      const float* row = proj + (size_t)(start + c0 + threadIdx.x) * proj_stride;
       xi = row[col_i + h];
       xf = row[col_f + h];
     }
   };
   float xi_next, xf_next;
   raw(0, xi_next, xf_next);
-  for (int c0 = 0; c0 < n; c0 += 32) {
-    const int t = start + c0 + lane;
-    const bool live = c0 + lane < n;
+  int buf = 0;
+  for (int c0 = 0; c0 < n; c0 += kGateWarps * 32, buf ^= 1) {
+    const int t = start + c0 + threadIdx.x;
+    const bool live = c0 + (int)threadIdx.x < n;
     const float xi = xi_next, xf = xf_next;
-    if (c0 + 32 < n) raw(c0 + 32, xi_next, xf_next);
-    float gi = 0.f, gf = 0.f;                    // the identity map for lanes past the end: F = 0, I = -inf
+    if (c0 + kGateWarps * 32 < n) raw(c0 + kGateWarps * 32, xi_next, xf_next);
+    float gi = 0.f, gf = 0.f;                    // the identity map for tokens past the end: F = 0, I = -inf
     if (live) {
       gi = cap * tanhf((xi + bi) / cap);
       gf = -softplus_f(-(cap * tanhf((xf + bf) / cap)));
     }
     float F = live ? gf : 0.f, I = live ? gi : -INFINITY;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {           // inclusive scan: the maps of tokens c0 .. c0 + lane composed
+    for (int o = 1; o < 32; o <<= 1) {           // inclusive scan: the maps of this warp's tokens up to the lane's
       const float F1 = __shfl_up_sync(0xffffffffu, F, o), I1 = __shfl_up_sync(0xffffffffu, I, o);
       if (lane >= o) { I = fmaxf(I1 + F, I); F = F1 + F; }
     }
-    const float m = fmaxf(m_in + F, I);
+    if (lane == 31) { F_s[buf][warp] = F; I_s[buf][warp] = I; }
+    __syncthreads();                             // (two buffers: the pass after writes the other one)
+    float m_warp = m_in;                         // m before this warp's first token
+#pragma unroll
+    for (int w = 0; w < kGateWarps; ++w) {
+      if (w == warp) m_warp = m_in;
+      m_in = fmaxf(m_in + F_s[buf][w], I_s[buf][w]);
+    }
+    const float m = fmaxf(m_warp + F, I);
     float m_prev = __shfl_up_sync(0xffffffffu, m, 1);
-    if (lane == 0) m_prev = m_in;
+    if (lane == 0) m_prev = m_warp;
     if (live) {
       a[(size_t)t * heads + h] = expf(gf + m_prev - m);
       b[(size_t)t * heads + h] = expf(gi - m);
       m_run[(size_t)t * heads + h] = m;
     }
-    m_in = __shfl_sync(0xffffffffu, m, 31);      // lanes past the end carry the last live value on
   }
-  if (write_state && lane == 0) *m_state = m_in;
+  if (write_state && threadIdx.x == 0) *m_state = m_in;
 }
 
 constexpr int kScanCols = 16;        // columns of S a block takes
@@ -349,26 +357,29 @@ ssm_out_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __re
     y[(size_t)t * inner + c0 + i] = from_f<T>(value(c0 + i) * rstd * w[c0 + i]);
 }
 
-// grid (tokens, heads).  o [T, heads * (vdim + 1)] from the scan with n.q in each head's last column, both
-// still to be multiplied by q_scale; y[t, h, j] = u / rms(u) * w[h vdim + j] * sigmoid(gate), u = o q_scale /
-// (max(|n.q| q_scale, exp(-m)) + 1e-6), gate = proj[t, col_g + h vdim + j].
+// A warp a token and head, 8 warps a block.  o [T, heads * (vdim + 1)] from the scan with n.q in each head's last
+// column, both still to be multiplied by q_scale; y[t, h, j] = u / rms(u) * w[h vdim + j] * sigmoid(gate),
+// u = o q_scale / (max(|n.q| q_scale, exp(-m)) + 1e-6), gate = proj[t, col_g + h vdim + j].
+constexpr int kOutWarps = 8;
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32 * kOutWarps)
 xlstm_out_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __restrict__ m_run,
                  const float* __restrict__ proj, int proj_stride, int col_g, const float* __restrict__ w,
-                 float eps, float q_scale, const int* __restrict__ positions, int heads, int vdim) {
-  __shared__ float scratch[33];
+                 float eps, float q_scale, const int* __restrict__ positions, int n_tokens, int heads, int vdim) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, h = blockIdx.y;
+  const int lane = threadIdx.x & 31;
+  const long long pair = (long long)blockIdx.x * kOutWarps + (threadIdx.x >> 5);
+  if (pair >= (long long)n_tokens * heads) return;
+  const int t = (int)(pair / heads), h = (int)(pair % heads);
   if (positions[t] < 0) return;
   const float* oh = o + ((size_t)t * heads + h) * (vdim + 1);
   const float den = fmaxf(fabsf(oh[vdim] * q_scale), expf(-m_run[(size_t)t * heads + h])) + 1e-6f;
   const float f = q_scale / den;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < vdim; i += blockDim.x) { const float u = oh[i] * f; ss += u * u; }
-  const float rstd = rsqrtf(block_sum(ss, scratch) / (float)vdim + eps);
-  for (int i = threadIdx.x; i < vdim; i += blockDim.x) {
+  for (int i = lane; i < vdim; i += 32) { const float u = oh[i] * f; ss += u * u; }
+  const float rstd = rsqrtf(warp_sum(ss) / (float)vdim + eps);
+  for (int i = lane; i < vdim; i += 32) {
     const int c = h * vdim + i;
     y[((size_t)t * heads) * vdim + c] =
         from_f<T>(oh[i] * f * rstd * w[c] * sigmoid_f(proj[(size_t)t * proj_stride + col_g + c]));
@@ -416,8 +427,8 @@ EK_EXPORT int ek_xgate_scan(float* a, float* b, float* m_run, const float* proj,
                             const int* token_slot, int n_seqs, int heads, int write_state, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (heads <= 0 || !(cap > 0.f)) return EK_ERR_ARG;
-  return (int)ek::launch_pdl(ek::xgate_scan_kernel, dim3(n_seqs, (heads + ek::kGateWarps - 1) / ek::kGateWarps),
-                             dim3(ek::kGateWarps * 32), 0, stream, a, b, m_run, proj, proj_stride, col_i, col_f,
+  if (heads > 65535) return EK_ERR_ARG;
+  return (int)ek::launch_pdl(ek::xgate_scan_kernel, dim3(n_seqs, heads), dim3(ek::kGateWarps * 32), 0, stream, a, b, m_run, proj, proj_stride, col_i, col_f,
                              bias_i, bias_f, cap, state, (size_t)slot_stride, (size_t)m_offset, cu_seqlens,
                              positions, token_slot, heads, write_state);
 }
@@ -467,8 +478,11 @@ EK_EXPORT int ek_decay_scan(float* out, int out_stride, const float* q, int q_st
                                       cudaStream_t stream) {                                                   \
     if (n_tokens <= 0) return 0;                                                                               \
     if (heads <= 0 || heads > 65535 || vdim <= 0) return EK_ERR_ARG;                                           \
-    return (int)ek::launch_pdl(ek::xlstm_out_kernel<T>, dim3(n_tokens, heads), dim3(128), 0, stream, (T*)y, o, \
-                               m_run, proj, proj_stride, col_g, w, eps, q_scale, positions, heads, vdim);      \
+    const long long blocks = ((long long)n_tokens * heads + ek::kOutWarps - 1) / ek::kOutWarps;                \
+    if (blocks > 0x7fffffffLL) return EK_ERR_ARG;                                                              \
+    return (int)ek::launch_pdl(ek::xlstm_out_kernel<T>, dim3((unsigned)blocks), dim3(32 * ek::kOutWarps), 0,   \
+                               stream, (T*)y, o, m_run, proj, proj_stride, col_g, w, eps, q_scale, positions,  \
+                               n_tokens, heads, vdim);                                                         \
   }
 
 EK_INSTANTIATE(f32, float)

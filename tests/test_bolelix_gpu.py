@@ -242,14 +242,14 @@ def test_convolution_with_carried_inputs(channels, taps):
 
 @pytest.mark.parametrize("heads,cap", [(2, 15.0), (5, 4.0), (3, 1.0)])
 def test_gates_with_their_running_maximum(heads, cap):
-    """a, b and m over three unequal sequences at once (one longer than the 32 tokens a pass takes), then
-    continued token by token from the carried maximum."""
+    """a, b and m over three unequal sequences at once (one of several passes of a block, one of a single
+    token, one just past a warp's 32 tokens), then continued token by token from the carried maximum."""
     k = K()
-    lens = [70, 1, 33]
+    lens = [600, 1, 33]
     n = sum(lens)
     proj = rnd(n, 2 * heads + 3, seed=1, scale=3.0)
     bi, bf = rnd(heads, seed=2), rnd(heads, seed=3) + 2.0
-    cu = [0, 70, 71, 104]
+    cu = [0, 600, 601, 634]
     pos = [p for m in lens for p in range(m)]
     slots = [s for s, m in zip((2, 0, 1), lens) for _ in range(m)]
     state = torch.zeros(3, 4 + heads, device=DEV)
@@ -266,7 +266,8 @@ def test_gates_with_their_running_maximum(heads, cap):
             want_a[t], want_b[t], want_m[t] = torch.exp(fg[t] + m - new), torch.exp(ig[t] - new), new
             m = new
     assert rel(a, want_a) <= 1e-5 and rel(b, want_b) <= 1e-5 and rel(m_run, want_m) <= 1e-5
-    assert rel(state[2, 4:], want_m[69]) <= 1e-5 and rel(state[0, 4:], want_m[70]) <= 1e-5
+    assert rel(state[2, 4:], want_m[599]) <= 1e-5 and rel(state[0, 4:], want_m[600]) <= 1e-5
+    assert rel(state[1, 4:], want_m[633]) <= 1e-5
     state.zero_()
     for t in range(40):                                                      # the first sequence again, one token a step
         k.xgate_scan(a[t:t + 1], b[t:t + 1], m_run[t:t + 1], proj[t:t + 1], 1, 1 + heads, bi, bf, cap, state, 4,
