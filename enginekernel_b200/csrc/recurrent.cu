@@ -334,6 +334,7 @@ decay_scan_kernel(float* __restrict__ out, int out_stride, const float* __restri
 
 // grid (tokens, parts).  y[t, c] = rms-normed over the part ((o + D[h] x) silu(z)) * w[c]; o [T, inner] from
 // the scan, x [T, .] the convolved inputs (stride x_stride), z = proj[t, col_z + c]; a head is vdim channels.
+constexpr int kOutKeep = 8;          // values a thread keeps in registers between the sum of squares and the write
 template <typename T>
 __global__ void __launch_bounds__(1024)
 ssm_out_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __restrict__ x, int x_stride,
@@ -351,6 +352,22 @@ ssm_out_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __re
     return (o[(size_t)t * inner + c] + d_skip[c / vdim] * x[(size_t)t * x_stride + c]) * (z * sigmoid_f(z));
   };
   float ss = 0.f;
+  if (size <= (int)blockDim.x * kOutKeep) {      // every value is fetched once and waits in a register for the norm
+    float u[kOutKeep];
+#pragma unroll
+    for (int m = 0; m < kOutKeep; ++m) {
+      const int i = threadIdx.x + m * blockDim.x;
+      u[m] = i < size ? value(c0 + i) : 0.f;
+      ss += u[m] * u[m];
+    }
+    const float rstd = rsqrtf(block_sum(ss, scratch) / (float)size + eps);
+#pragma unroll
+    for (int m = 0; m < kOutKeep; ++m) {
+      const int i = threadIdx.x + m * blockDim.x;
+      if (i < size) y[(size_t)t * inner + c0 + i] = from_f<T>(u[m] * rstd * w[c0 + i]);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < size; i += blockDim.x) { const float u = value(c0 + i); ss += u * u; }
   const float rstd = rsqrtf(block_sum(ss, scratch) / (float)size + eps);
   for (int i = threadIdx.x; i < size; i += blockDim.x)
@@ -377,6 +394,23 @@ xlstm_out_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __
   const float den = fmaxf(fabsf(oh[vdim] * q_scale), expf(-m_run[(size_t)t * heads + h])) + 1e-6f;
   const float f = q_scale / den;
   float ss = 0.f;
+  if (vdim <= 32 * kOutKeep) {                   // the head's values and gates are fetched once, all at a time
+    float u[kOutKeep], g[kOutKeep];
+#pragma unroll
+    for (int m = 0; m < kOutKeep; ++m) {
+      const int i = lane + 32 * m;
+      u[m] = i < vdim ? oh[i] * f : 0.f;
+      g[m] = i < vdim ? proj[(size_t)t * proj_stride + col_g + h * vdim + i] : 0.f;
+      ss += u[m] * u[m];
+    }
+    const float rstd = rsqrtf(warp_sum(ss) / (float)vdim + eps);
+#pragma unroll
+    for (int m = 0; m < kOutKeep; ++m) {
+      const int i = lane + 32 * m, c = h * vdim + i;
+      if (i < vdim) y[((size_t)t * heads) * vdim + c] = from_f<T>(u[m] * rstd * w[c] * sigmoid_f(g[m]));
+    }
+    return;
+  }
   for (int i = lane; i < vdim; i += 32) { const float u = oh[i] * f; ss += u * u; }
   const float rstd = rsqrtf(warp_sum(ss) / (float)vdim + eps);
   for (int i = lane; i < vdim; i += 32) {
