@@ -201,6 +201,42 @@ __global__ void add_scaled_kernel(float* __restrict__ resid, const T* __restrict
   if (b) add = fmaf(to_f<T>(b[i]), sb ? sb[c] : 1.f, add);
   resid[i] += add;
 }
+// the same, four neighbours a thread (hidden a multiple of 4, every row on a 16-byte boundary)
+template <typename T>
+__global__ void add_scaled4_kernel(float* __restrict__ resid, const T* __restrict__ a, const float* __restrict__ sa,
+                                   const T* __restrict__ b, const float* __restrict__ sb, size_t n4, int hidden4) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const int c = (int)(i % hidden4);
+  const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+  const float4 fa = sa ? reinterpret_cast<const float4*>(sa)[c] : one, fb = sb ? reinterpret_cast<const float4*>(sb)[c] : one;
+  float4 r = reinterpret_cast<float4*>(resid)[i];
+  float va[4], vb[4] = {0.f, 0.f, 0.f, 0.f};
+  if (sizeof(T) == 2) {
+    const uint2 pa = reinterpret_cast<const uint2*>(a)[i];
+    const T* ta = reinterpret_cast<const T*>(&pa);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) va[j] = to_f<T>(ta[j]);
+    if (b) {
+      const uint2 pb = reinterpret_cast<const uint2*>(b)[i];
+      const T* tb = reinterpret_cast<const T*>(&pb);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) vb[j] = to_f<T>(tb[j]);
+    }
+  } else {
+    const float4 pa = reinterpret_cast<const float4*>(a)[i];
+    va[0] = pa.x, va[1] = pa.y, va[2] = pa.z, va[3] = pa.w;
+    if (b) {
+      const float4 pb = reinterpret_cast<const float4*>(b)[i];
+      vb[0] = pb.x, vb[1] = pb.y, vb[2] = pb.z, vb[3] = pb.w;
+    }
+  }
+  r.x += fmaf(vb[0], fb.x, va[0] * fa.x);
+  r.y += fmaf(vb[1], fb.y, va[1] * fa.y);
+  r.z += fmaf(vb[2], fb.z, va[2] * fa.z);
+  r.w += fmaf(vb[3], fb.w, va[3] * fa.w);
+  reinterpret_cast<float4*>(resid)[i] = r;
+}
 
 // out[r, i] = act(gu[r, i]) * gu[r, inter + i]    (silu: engine/ek_kernels.py:125-143)
 // VEC: inter is a multiple of 4; a thread handles four neighbours.  A 16-bit result takes the
@@ -358,8 +394,14 @@ using namespace ek;
                                        const float* sb, long long n, int hidden, cudaStream_t stream) { \
     if (n <= 0) return 0;                                                                       \
     if (hidden <= 0 || a == nullptr) return EK_ERR_ARG;                                         \
-    add_scaled_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(                      \
-        resid, (const T*)a, sa, (const T*)b, sb, (size_t)n, hidden);                            \
+    const uintptr_t bits = (uintptr_t)resid | (uintptr_t)sa | (uintptr_t)sb |                   \
+                           (((uintptr_t)a | (uintptr_t)b) * (16 / (4 * sizeof(T))));            \
+    if (hidden % 4 == 0 && (bits & 15) == 0)                                                    \
+      add_scaled4_kernel<T><<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>(               \
+          resid, (const T*)a, sa, (const T*)b, sb, (size_t)n / 4, hidden / 4);                  \
+    else                                                                                        \
+      add_scaled_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(                    \
+          resid, (const T*)a, sa, (const T*)b, sb, (size_t)n, hidden);                          \
     EK_RETURN_LAUNCH_STATUS();                                                                  \
   }                                                                                             \
   EK_EXPORT int ek_silu_mul_##SUFFIX(void* out, const void* gu, int rows, int inter,            \

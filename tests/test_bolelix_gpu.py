@@ -32,7 +32,7 @@ def i32(x):
 
 # ===================================================================== mechanisms alone
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,width", [(1, 40), (17, 100), (5, 96), (33, 2560)])
+@pytest.mark.parametrize("rows,width", [(1, 40), (17, 100), (5, 96), (3, 50), (33, 2560)])
 def test_scaled_sum_into_the_stream_and_norm(dtype, rows, width):
     k = K()
     stream = rnd(rows, width, seed=1)
