@@ -73,19 +73,23 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
                                          int keys_per_split, float* __restrict__ part_acc,
                                          float* __restrict__ part_ml, float sink,
                                          const float* __restrict__ sinks, int keep_first,
-                                         const T* __restrict__ gate, int gate_stride) {
+                                         const T* __restrict__ gate, int gate_stride, int cross,
+                                         float* __restrict__ out32) {
   __shared__ float q_s[kGenericMaxDim];
   __shared__ float p_s[kAttnThreads];
   __shared__ size_t voff_s[kAttnThreads];
   __shared__ float scratch[33];
 
-  const int t = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+  // cross > 1: grid.y runs over (query head, value head) pairs - the head's softmax weights, taken
+  // against its own key head, are applied to the values of EVERY key/value head in turn
+  const int t = blockIdx.x, h = blockIdx.y / cross, split = blockIdx.z;
   const int tid = threadIdx.x;
   if (sinks != nullptr) sink = sinks[h];        // a sink score of its own for every query head
   const int d = cache.head_dim;
   const int kv_head = h / (n_q_heads / cache.heads);
+  const int v_head = cross > 1 ? (int)(blockIdx.y % cross) : kv_head;
   const int pos = positions[t];
-  const size_t part_index = ((size_t)t * n_q_heads + h) * n_splits + split;
+  const size_t part_index = ((size_t)t * gridDim.y + blockIdx.y) * n_splits + split;
 
   int lo = 0, hi = -1;                          // keys [lo, hi] ...
   int f_lo = 0, f_hi = -1;                      // ... and the kept first keys [f_lo, f_hi] before them
@@ -121,9 +125,9 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
       const bool seen = x < total;
       float s = -INFINITY;
       if (seen) {
-        const size_t off = page_offset(cache, table[j / EK_PAGE], kv_head, j);
-        voff_s[tid] = off;
-        s = dot_row<T>(kbase + off, q_s, d);
+        const int page = table[j / EK_PAGE];
+        voff_s[tid] = page_offset(cache, page, v_head, j);
+        s = dot_row<T>(kbase + page_offset(cache, page, kv_head, j), q_s, d);
       }
       const float m_new = fmaxf(m, block_max(s, scratch));
       const float p = seen ? expf(s - m_new) : 0.f;
@@ -146,14 +150,17 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
   }
 
   if (n_splits == 1) {
-    T* orow = out + ((size_t)t * n_q_heads + h) * d;
+    const size_t o_at = ((size_t)t * gridDim.y + blockIdx.y) * d;
     // a sink: one more term exp(sink) in the denominator, with no value (-inf: none)
     if (sink > -INFINITY && l > 0.f) l += expf(sink - m);
     float inv = l > 0.f ? 1.f / l : 0.f;
     if (gate != nullptr) inv *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)t * gate_stride + h])));
 #pragma unroll
     for (int a = 0; a < kGenericAcc; ++a)
-      if (tid + a * kAttnThreads < d) orow[tid + a * kAttnThreads] = from_f<T>(acc[a] * inv);
+      if (tid + a * kAttnThreads < d) {
+        if (out32) out32[o_at + tid + a * kAttnThreads] = acc[a] * inv;
+        else out[o_at + tid + a * kAttnThreads] = from_f<T>(acc[a] * inv);
+      }
   } else {
     float* pa = part_acc + part_index * d;
 #pragma unroll
@@ -172,9 +179,10 @@ __global__ void attention_combine_kernel(T* __restrict__ out, const float* __res
                                          const float* __restrict__ part_ml, int n_q_heads,
                                          int head_dim, int n_splits, float sink,
                                          const float* __restrict__ sinks, const T* __restrict__ gate,
-                                         int gate_stride) {
-  if (sinks != nullptr) sink = sinks[blockIdx.y];
-  const size_t th = (size_t)blockIdx.x * n_q_heads + blockIdx.y;
+                                         int gate_stride, int cross, float* __restrict__ out32) {
+  const int h = blockIdx.y / cross;
+  if (sinks != nullptr) sink = sinks[h];
+  const size_t th = (size_t)blockIdx.x * gridDim.y + blockIdx.y;
   const float* ml = part_ml + 2 * th * n_splits;
   float m = -INFINITY;
   for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
@@ -183,12 +191,13 @@ __global__ void attention_combine_kernel(T* __restrict__ out, const float* __res
     if (ml[2 * s + 1] > 0.f) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
   if (sink > -INFINITY && l > 0.f) l += expf(sink - m);                 // the sink, counted once
   float inv = l > 0.f ? 1.f / l : 0.f;
-  if (gate != nullptr) inv *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)blockIdx.x * gate_stride + blockIdx.y])));
+  if (gate != nullptr) inv *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)blockIdx.x * gate_stride + h])));
   for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < n_splits; ++s)
       if (ml[2 * s + 1] > 0.f) acc += part_acc[(th * n_splits + s) * head_dim + i] * expf(ml[2 * s] - m);
-    out[th * head_dim + i] = from_f<T>(acc * inv);
+    if (out32) out32[th * head_dim + i] = acc * inv;
+    else out[th * head_dim + i] = from_f<T>(acc * inv);
   }
 }
 
@@ -199,25 +208,56 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
                   int n_kv_heads, int head_dim, float scale, int window, int n_splits,
                   int keys_per_split, float* part_acc, float* part_ml, float sink,
                   const float* sinks, int keep_first, const void* gate, int gate_stride,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, int cross = 1, float* out32 = nullptr) {
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim > kGenericMaxDim || n_kv_heads <= 0 ||
       n_q_heads % n_kv_heads || n_q_heads > 65535 || n_splits < 1 || n_splits > 65535 ||
-      (n_splits > 1 && (!part_acc || !part_ml || keys_per_split <= 0)))
+      (n_splits > 1 && (!part_acc || !part_ml || keys_per_split <= 0)) ||
+      (cross != 1 && cross != n_kv_heads) || (long long)n_q_heads * cross > 65535)
     return EK_ERR_ARG;
   PagedKV cache{(void*)k_pages, (void*)v_pages, block_table, table_stride, n_kv_heads, head_dim};
-  dim3 grid(n_tokens, n_q_heads, n_splits);
+  dim3 grid(n_tokens, n_q_heads * cross, n_splits);
   attention_generic_kernel<T><<<grid, kAttnThreads, 0, stream>>>(
       (T*)out, (const T*)q, q_row_stride, positions, token_slot, cache, n_q_heads, scale, window,
       n_splits, keys_per_split, part_acc, part_ml, sink, sinks, window > 0 ? keep_first : 0,
-      (const T*)gate, gate_stride);
+      (const T*)gate, gate_stride, cross, out32);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || n_splits == 1) return (int)e;
-  dim3 cgrid(n_tokens, n_q_heads);
+  dim3 cgrid(n_tokens, n_q_heads * cross);
   attention_combine_kernel<T><<<cgrid, 64, 0, stream>>>((T*)out, part_acc, part_ml, n_q_heads,
                                                         head_dim, n_splits, sink, sinks,
-                                                        (const T*)gate, gate_stride);
+                                                        (const T*)gate, gate_stride, cross, out32);
   EK_RETURN_LAUNCH_STATUS();
+}
+
+// Heads that share their softmax weights ("talking heads" behind the softmax): with
+// weight_h <- sum_g mix[h, g] weight_g and head h applying its mixed weights to the values of its own
+// key/value head c(h) = h / (H / G), the result is  out_h = sum_g mix[h, g] * A[g, c(h)],  A[g, c] being
+// head g's weights applied to value head c - what the attention kernels above write with cross = G
+// (32-bit, [T, H, G, head size]).  This kernel forms the sums, multiplies element by element by the
+// sigmoid of a gate row (optional) and rounds: out [T, H * vdim].  grid: tokens.
+template <typename T>
+__global__ void mix_heads_kernel(T* __restrict__ out, const float* __restrict__ parts, const float* __restrict__ mix,
+                                 const T* __restrict__ gate, int gate_stride, int n_q_heads, int n_kv_heads,
+                                 int head_dim, int vdim, const int* __restrict__ positions) {
+  extern __shared__ float mix_s[];              // [H][H]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < n_q_heads * n_q_heads; i += blockDim.x) mix_s[i] = mix[i];
+  __syncthreads();
+  const bool live = positions[t] >= 0;
+  const int per = n_q_heads / n_kv_heads;
+  const float* a = parts + (size_t)t * n_q_heads * n_kv_heads * head_dim;
+  for (int i = threadIdx.x; i < n_q_heads * vdim; i += blockDim.x) {
+    const int h = i / vdim, j = i % vdim, c = h / per;
+    float acc = 0.f;
+    if (live)
+      for (int g = 0; g < n_q_heads; ++g)
+        acc = fmaf(mix_s[h * n_q_heads + g], a[((size_t)g * n_kv_heads + c) * head_dim + j], acc);
+    if (gate != nullptr && live) acc *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)t * gate_stride + i])));
+    out[(size_t)t * n_q_heads * vdim + i] = from_f<T>(acc);
+  }
 }
 
 }  // namespace ek
@@ -236,5 +276,34 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
                          sinks, keep_first, gate, gate_stride, stream);                        \
   }
 
+#define EK_INSTANTIATE_CROSS(SUFFIX, T)                                                        \
+  /* Every query head's weights applied to the values of every key/value head: out32          */ \
+  /* [T, heads, kv heads, head size] in 32-bit (see mix_heads_kernel).                        */ \
+  EK_EXPORT int ek_attention_generic_cross_##SUFFIX(                                            \
+      float* out32, const void* q, int q_row_stride, const int* positions, const int* token_slot, \
+      const void* k_pages, const void* v_pages, const int* block_table, int table_stride,      \
+      int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, float scale, int window,      \
+      int n_splits, int keys_per_split, float* part_acc, float* part_ml, int keep_first,       \
+      cudaStream_t stream) {                                                                   \
+    if (!out32) return EK_ERR_ARG;                                                             \
+    return ek::launch<T>(nullptr, q, q_row_stride, positions, token_slot, k_pages, v_pages,    \
+                         block_table, table_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, \
+                         scale, window, n_splits, keys_per_split, part_acc, part_ml, -INFINITY, \
+                         nullptr, keep_first, nullptr, 0, stream, n_kv_heads, out32);          \
+  }                                                                                            \
+  EK_EXPORT int ek_mix_heads_##SUFFIX(void* out, const float* parts, const float* mix, const void* gate, \
+                                      int gate_stride, const int* positions, int n_tokens, int n_q_heads, \
+                                      int n_kv_heads, int head_dim, int vdim, cudaStream_t stream) { \
+    if (n_tokens <= 0) return 0;                                                               \
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || vdim <= 0 || vdim > head_dim || \
+        n_q_heads > 96 || (gate && gate_stride < n_q_heads * vdim))                            \
+      return EK_ERR_ARG;                                                                       \
+    return (int)ek::launch_pdl(ek::mix_heads_kernel<T>, dim3(n_tokens), dim3(256),             \
+                               (size_t)n_q_heads * n_q_heads * sizeof(float), stream, (T*)out, parts, mix, \
+                               (const T*)gate, gate_stride, n_q_heads, n_kv_heads, head_dim, vdim, positions); \
+  }
+
 EK_INSTANTIATE(f32, float)
 EK_INSTANTIATE(bf16, ek::bf16)
+EK_INSTANTIATE_CROSS(f32, float)
+EK_INSTANTIATE_CROSS(bf16, ek::bf16)

@@ -1,4 +1,4 @@
-// Gated delta rule with one decay per key channel, as a recurrent mixer with per-sequence state.
+// Gated delta rule with one decay per key channel (or one per head), as a recurrent mixer with per-sequence state.
 //
 // Per token and head (S is [d, e], 32-bit, carried from token to token):
 //     S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
@@ -240,7 +240,7 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, const f
                   const float* __restrict__ vc, const float* __restrict__ beta,
                   const float* __restrict__ decay, float* __restrict__ state, size_t slot_stride,
                   const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
-                  const int* __restrict__ token_slot, DeltaShape sh) {
+                  const int* __restrict__ token_slot, DeltaShape sh, int decay_per_head) {
   constexpr int DP = RPL * kScanLanes;          // rows held (>= dim; rows past dim stay zero)
   constexpr int LDS = RPL + 4;                  // a lane's stretch in shared memory, padded
   constexpr int ROW = kScanLanes * LDS;
@@ -283,7 +283,7 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, const f
       const size_t rowi = (size_t)(start + c0 + tt);
       rq[i] = ok ? qn[rowi * cq + (size_t)kvh * sh.dim + r] : 0.f;
       rk[i] = ok ? kn[rowi * cq + (size_t)kvh * sh.dim + r] : 0.f;
-      rg[i] = ok ? decay[rowi * nd + (size_t)h * sh.dim + r] : 1.f;
+      rg[i] = ok ? (decay_per_head ? decay[rowi * sh.heads + h] : decay[rowi * nd + (size_t)h * sh.dim + r]) : 1.f;
     }
 #pragma unroll
     for (int i = 0; i < PERV; ++i) {
@@ -373,7 +373,7 @@ template <int RPL>
 static cudaError_t launch_scan(dim3 grid, cudaStream_t stream, float* out, const float* qn, const float* kn,
                                const float* vc, const float* beta, const float* decay, float* state,
                                size_t slot_stride, const int* cu_seqlens, const int* positions,
-                               const int* token_slot, DeltaShape sh) {
+                               const int* token_slot, DeltaShape sh, int decay_per_head) {
   constexpr int ROW = kScanLanes * (RPL + 4);
   const size_t smem = sizeof(float) * (size_t)(6 * kScanChunk * ROW + 2 * kScanChunk * kScanCols + 2 * kScanChunk +
                                                kScanChunk * kScanCols);
@@ -382,16 +382,17 @@ static cudaError_t launch_scan(dim3 grid, cudaStream_t stream, float* out, const
     if (e != cudaSuccess) return e;
   }
   delta_scan_kernel<RPL><<<grid, kScanThreads, smem, stream>>>(out, qn, kn, vc, beta, decay, state, slot_stride,
-                                                              cu_seqlens, positions, token_slot, sh);
+                                                              cu_seqlens, positions, token_slot, sh, decay_per_head);
   return cudaGetLastError();
 }
 
-// grid: tokens.  y[t, h, j] = o[t, h, j] / rms_j(o[t, h, :]) * w[j] * gate[t, h, j].
+// grid: tokens.  y[t, h, j] = o[t, h, j] / rms_j(o[t, h, :]) * w[j] * f(gate[t, h, j]); gate rows are
+// `gate_stride` apart; f is the identity (gate_act 0: the gate is finished) or SiLU (1: it is a raw projection).
 template <typename T>
 __global__ void __launch_bounds__(256)
 delta_out_norm_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __restrict__ gate,
                       const float* __restrict__ w, float eps, const int* __restrict__ positions,
-                      DeltaShape sh) {
+                      DeltaShape sh, int gate_stride, int gate_act) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, tid = threadIdx.x;
@@ -409,7 +410,9 @@ delta_out_norm_kernel(T* __restrict__ y, const float* __restrict__ o, const floa
     const float inv = rsqrtf(ss / (float)sh.vdim + eps);
     for (int j = lane; j < sh.vdim; j += 32) {
       const int c = h * sh.vdim + j;
-      y[(size_t)t * cv + c] = from_f<T>(x[j] * inv * w[j] * gate[(size_t)t * cv + c]);
+      float g = gate[(size_t)t * gate_stride + c];
+      if (gate_act == 1) g = g * sigmoid_f(g);
+      y[(size_t)t * cv + c] = from_f<T>(x[j] * inv * w[j] * g);
     }
   }
 }
@@ -496,7 +499,8 @@ EK_EXPORT int ek_delta_conv_tail(float* state, long long slot_stride, long long 
 EK_EXPORT int ek_delta_scan(float* out, const float* qn, const float* kn, const float* vc,
                             const float* beta, const float* decay, float* state, long long slot_stride,
                             const int* cu_seqlens, const int* positions, const int* token_slot,
-                            int n_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
+                            int n_seqs, int heads, int kv_heads, int dim, int vdim, int decay_per_head,
+                            cudaStream_t stream) {
   using namespace ek;
   if (n_seqs <= 0) return 0;
   DeltaShape sh{heads, kv_heads, dim, vdim, 1, 1, 1};
@@ -507,7 +511,7 @@ EK_EXPORT int ek_delta_scan(float* out, const float* qn, const float* kn, const 
   const int rows = ek_delta_state_rows(dim);
 #define EK_SCAN(RPL)                                                                                 \
   return (int)launch_scan<RPL>(grid, stream, out, qn, kn, vc, beta, decay, state, (size_t)slot_stride, \
-                               cu_seqlens, positions, token_slot, sh)
+                               cu_seqlens, positions, token_slot, sh, decay_per_head)
   switch (rows) {
     case 32: EK_SCAN(4);
     case 64: EK_SCAN(8);
@@ -523,12 +527,14 @@ EK_EXPORT int ek_delta_scan(float* out, const float* qn, const float* kn, const 
                                            const float* w, float eps,                                \
                                            const int* positions, int n_tokens, int heads,            \
                                            int kv_heads, int dim, int vdim, int taps, int rank_a,    \
-                                           int rank_g, cudaStream_t stream) {                        \
+                                           int rank_g, int gate_stride, int gate_act,                \
+                                           cudaStream_t stream) {                                    \
     using namespace ek;                                                                              \
     if (n_tokens <= 0) return 0;                                                                     \
     DeltaShape sh{heads, kv_heads, dim, vdim, taps, rank_a, rank_g};                                 \
-    if (!shape_ok(sh)) return EK_ERR_ARG;                                                            \
-    delta_out_norm_kernel<T><<<n_tokens, 256, 0, stream>>>((T*)y, o, gate, w, eps, positions, sh);   \
+    if (!shape_ok(sh) || gate_stride < sh.cv() || gate_act < 0 || gate_act > 1) return EK_ERR_ARG;   \
+    delta_out_norm_kernel<T><<<n_tokens, 256, 0, stream>>>((T*)y, o, gate, w, eps, positions, sh,    \
+                                                           gate_stride, gate_act);                   \
     EK_RETURN_LAUNCH_STATUS();                                                                       \
   }
 

@@ -1,5 +1,6 @@
-// Embedding lookup, RMSNorm (plain, with the residual add folded in, and on
-// gathered rows) and the SwiGLU gate.
+// Embedding lookup (also through a hashed table of token pairs), RMSNorm (plain, with the residual add
+// folded in, on gathered rows, behind a sum of scaled results, and as the pair "norm of a result, add,
+// norm of the stream"), the SwiGLU gate, and bias + activation on a projection's rows.
 //
 // The residual stream is held in 32-bit in both precisions; T is the type of the
 // normalised activations that feed the matrix products (float or bfloat16).
@@ -255,6 +256,116 @@ __device__ __forceinline__ float silu_of(float g) {
   return g / (1.f + expf(-g));
 }
 
+// resid[t] += table[row], row = (previous * mul_prev + ids[t] * mul_cur) mod buckets, or row `buckets`
+// (the table's last) for a sequence's first token.  The token before t is the step's token t - 1 when
+// that belongs to the same sequence, else what the sequence's slot holds in `before` (a 32-bit integer
+// per slot, `before_stride` apart).  A plain launch; rows whose position is negative are skipped.
+template <typename T>
+__global__ void embed_pair_kernel(float* __restrict__ resid, const T* __restrict__ table, const int* ids,
+                                  const int* positions, const int* token_slot, const int* before,
+                                  long long before_stride, int hidden, int buckets, long long mul_prev,
+                                  long long mul_cur) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  int row = buckets;
+  if (pos > 0) {
+    const int slot = token_slot[t];
+    const int prev = (t > 0 && token_slot[t - 1] == slot && positions[t - 1] == pos - 1)
+                         ? ids[t - 1] : before[(size_t)slot * before_stride];
+    row = (int)(((long long)prev * mul_prev + (long long)ids[t] * mul_cur) % (long long)buckets);
+  }
+  const T* src = table + (size_t)row * hidden;
+  float* out = resid + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] += to_f<T>(src[i]);
+}
+
+// before[slot] = the last token a sequence brought in this step.
+__global__ void keep_last_token_kernel(int* before, long long before_stride, const int* ids, const int* positions,
+                                       const int* token_slot, int n_tokens) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tokens || positions[t] < 0) return;
+  const int slot = token_slot[t];
+  if (t + 1 < n_tokens && token_slot[t + 1] == slot && positions[t + 1] == positions[t] + 1) return;
+  before[(size_t)slot * before_stride] = ids[t];
+}
+
+// dst[r, col0 + i] = src[r, i] rounded to T, for i < width (dst rows `dst_stride` apart).
+template <typename T>
+__global__ void cast_columns_kernel(T* __restrict__ dst, int dst_stride, int col0, const float* __restrict__ src,
+                                    int width, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t r = i / width;
+  const int c = (int)(i % width);
+  dst[r * dst_stride + col0 + c] = from_f<T>(src[i]);
+}
+
+// A sublayer's result passes a norm of its own before it joins the stream, and the norm of the next
+// reader follows in the same pass over the row:
+//     u = a * wa + b * wb + bias          (b, bias optional; wa, wb plain numbers)
+//     stream += gain_post * u * rsqrt(mean(u^2) + eps_post)
+//     y = gain * stream * rsqrt(mean(stream^2) + eps)          (only when y is given)
+// A block a row, the row in shared memory (2 x hidden floats).
+template <typename T>
+__global__ void rmsnorm_post_add_kernel(T* __restrict__ y, float* resid, const T* __restrict__ a, float wa,
+                                        const T* __restrict__ b, float wb, const float* __restrict__ bias,
+                                        const float* __restrict__ gain_post, float eps_post,
+                                        const float* __restrict__ gain, float eps, int hidden) {
+  __shared__ float scratch[33];
+  extern __shared__ __align__(16) float row_cache[];          // u, then the stream's row
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  float* r = resid + row * hidden;
+  const T* ar = a + row * hidden;
+  const T* br = b ? b + row * hidden : nullptr;
+  float* u_s = row_cache;
+  float* x_s = row_cache + hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float u = to_f<T>(ar[i]) * wa;
+    if (br) u = fmaf(to_f<T>(br[i]), wb, u);
+    if (bias) u += bias[i];
+    u_s[i] = u;
+    x_s[i] = r[i];
+    ss += u * u;
+  }
+  const float rstd_post = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps_post);
+  ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = x_s[i] + u_s[i] * rstd_post * gain_post[i];
+    r[i] = v;
+    x_s[i] = v;
+    ss += v * v;
+  }
+  if (y == nullptr) return;
+  const float rstd = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+  T* out = y + row * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = from_f<T>(x_s[i] * rstd * gain[i]);
+}
+
+// out[r, i] = act(x[r, col0 + i] + bias[i]) for i < width; act 0: none, 1: the tanh form of GELU, 2: SiLU.
+// x is 32-bit or T (`x_is_f32`), rows `x_stride` apart.
+template <typename T>
+__global__ void bias_act_kernel(T* __restrict__ out, const void* __restrict__ x, int x_is_f32, int x_stride,
+                                int col0, const float* __restrict__ bias, int width, size_t n, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t r = i / width;
+  const int c = (int)(i % width);
+  const size_t at = r * x_stride + col0 + c;
+  float v = x_is_f32 ? ((const float*)x)[at] : to_f<T>(((const T*)x)[at]);
+  if (bias) v += bias[c];
+  if (act == 1) v = silu_of<T, 1>(v);
+  else if (act == 2) v = silu_of<T, 0>(v);
+  out[i] = from_f<T>(v);
+}
+
 template <typename T, bool VEC, int ACT>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter) {
   const size_t r = blockIdx.y;
@@ -383,6 +494,51 @@ using namespace ek;
                                (const T*)a, sa, (const T*)b, sb, gain, rows, eps, hidden,       \
                                write_back);                                                     \
   }                                                                                             \
+  EK_EXPORT int ek_embed_pair_##SUFFIX(float* resid, const void* table, const int* ids,           \
+                                       const int* positions, const int* token_slot, const int* before, \
+                                       long long before_stride, int n_tokens, int hidden, int buckets, \
+                                       long long mul_prev, long long mul_cur, cudaStream_t stream) { \
+    if (n_tokens <= 0) return 0;                                                                \
+    if (buckets <= 0 || mul_prev < 0 || mul_cur < 0 || hidden <= 0) return EK_ERR_ARG;          \
+    embed_pair_kernel<T><<<dim3(n_tokens), dim3(256), 0, stream>>>(resid, (const T*)table, ids, positions, \
+                                                                    token_slot, before, before_stride, \
+                                                                    hidden, buckets, mul_prev, mul_cur); \
+    EK_RETURN_LAUNCH_STATUS();                                                                  \
+  }                                                                                             \
+  EK_EXPORT int ek_cast_columns_##SUFFIX(void* dst, int dst_stride, int col0, const float* src, int width, \
+                                         int n_rows, cudaStream_t stream) {                     \
+    if (n_rows <= 0) return 0;                                                                  \
+    if (width <= 0 || col0 < 0 || dst_stride < col0 + width) return EK_ERR_ARG;                 \
+    const size_t n = (size_t)n_rows * width;                                                    \
+    return (int)ek::launch_pdl(ek::cast_columns_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, \
+                               stream, (T*)dst, dst_stride, col0, src, width, n);               \
+  }                                                                                             \
+  EK_EXPORT int ek_rmsnorm_post_add_##SUFFIX(void* y, float* resid, const void* a, float wa, const void* b, \
+                                             float wb, const float* bias, const float* gain_post, \
+                                             float eps_post, const float* gain, float eps, int n_rows, \
+                                             int hidden, cudaStream_t stream) {                 \
+    if (n_rows <= 0) return 0;                                                                  \
+    if (hidden <= 0 || (size_t)hidden * 8 > 200 * 1024 || a == nullptr || gain_post == nullptr || \
+        (y != nullptr && gain == nullptr))                                                      \
+      return EK_ERR_ARG;                                                                        \
+    const size_t smem = (size_t)hidden * 2 * sizeof(float);                                     \
+    auto kernel = ek::rmsnorm_post_add_kernel<T>;                                               \
+    if (smem > 40 * 1024) {                                                                     \
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                      \
+    }                                                                                           \
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);                     \
+    return (int)ek::launch_pdl(kernel, dim3(n_rows), dim3(threads), smem, stream, (T*)y, resid, \
+                               (const T*)a, wa, (const T*)b, wb, bias, gain_post, eps_post, gain, eps, hidden); \
+  }                                                                                             \
+  EK_EXPORT int ek_bias_act_##SUFFIX(void* out, const void* x, int x_is_f32, int x_stride, int col0, \
+                                     const float* bias, int width, int n_rows, int act, cudaStream_t stream) { \
+    if (n_rows <= 0) return 0;                                                                  \
+    if (width <= 0 || col0 < 0 || x_stride < col0 + width || act < 0 || act > 2) return EK_ERR_ARG; \
+    const size_t n = (size_t)n_rows * width;                                                    \
+    return (int)ek::launch_pdl(ek::bias_act_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, \
+                               stream, (T*)out, x, x_is_f32, x_stride, col0, bias, width, n, act); \
+  }                                                                                             \
   EK_EXPORT int ek_add_residual_##SUFFIX(float* resid, const void* add, long long n,            \
                                          cudaStream_t stream) {                                 \
     if (n <= 0) return 0;                                                                       \
@@ -418,6 +574,15 @@ using namespace ek;
 
 EK_INSTANTIATE(f32, float)
 EK_INSTANTIATE(bf16, ek::bf16)
+
+// before[slot] = the last token every sequence of the step brought (see embed_pair_kernel)
+EK_EXPORT int ek_keep_last_token(int* before, long long before_stride, const int* ids, const int* positions,
+                                 const int* token_slot, int n_tokens, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  ek::keep_last_token_kernel<<<(unsigned)((n_tokens + 255) / 256), 256, 0, stream>>>(before, before_stride, ids,
+                                                                                      positions, token_slot, n_tokens);
+  EK_RETURN_LAUNCH_STATUS();
+}
 
 // x[i] *= scale for n 32-bit values (logits of a model with a logit multiplier)
 EK_EXPORT int ek_scale_f32(float* x, long long n, float scale, cudaStream_t stream) {

@@ -19,6 +19,9 @@
 //   decay_scan       the recurrence; reads and writes S in the state
 //   ssm_out          (o + D x) silu(z), RMS norm in equal parts, weight -> activation type
 //   xlstm_out        o / (max(|n.q|, exp(-m)) + 1e-6), RMS norm per head, weight, sigmoid gate
+// and a recurrence with a decay per CHANNEL and no matrix state (a gated linear recurrent unit):
+//   lru_gates        both gates from block-diagonal products, the decay and the gated input
+//   lru_scan         S_t = a_t S_(t-1) + x_t per channel, times the GELU of a side branch
 // Everything here is 32-bit; only the two output kernels round, once, to the activation type.
 #include "common.cuh"
 
@@ -37,7 +40,7 @@ __device__ __forceinline__ int step_predecessors(const int* positions, const int
 }
 
 // grid (token tiles, channel tiles).  out[t, c] = silu(bias[c] + sum_j w[c][K-1-j] x[t-j, c]) with
-// x = proj[., col0 + c].  tail of a slot: [channels][K-1], oldest first.  A block takes `per_block`
+// x = proj[., col0 + c] (+ in_bias[c] for tokens that exist; `act` 0: no SiLU).  tail of a slot: [channels][K-1], oldest first.  A block takes `per_block`
 // neighbouring tokens (at most 16), so that a prompt's rows are fetched once into L1 for all their taps.
 constexpr int kConvTokens = 16;
 __global__ void __launch_bounds__(256)
@@ -45,8 +48,8 @@ conv_silu_kernel(float* __restrict__ out, int out_stride, const float* __restric
                  const float* __restrict__ conv_w, const float* __restrict__ conv_b,
                  const float* __restrict__ state, size_t slot_stride, size_t tail_offset,
                  const int* __restrict__ positions, const int* __restrict__ token_slot, int n_tokens, int channels,
-                 int K, int per_block) {
-  __shared__ int n_prev_s[kConvTokens], slot_s[kConvTokens];
+                 int K, int per_block, const float* __restrict__ in_bias, int act) {
+  __shared__ int n_prev_s[kConvTokens], slot_s[kConvTokens], pos_s[kConvTokens];
   pdl_launch_dependents();
   pdl_wait();
   const int t0 = blockIdx.x * per_block, nt = min(per_block, n_tokens - t0);
@@ -55,22 +58,25 @@ conv_silu_kernel(float* __restrict__ out, int out_stride, const float* __restric
     const bool live = positions[t] >= 0;
     n_prev_s[threadIdx.x] = live ? step_predecessors(positions, token_slot, t, K - 1) : -1;
     slot_s[threadIdx.x] = live ? token_slot[t] : 0;
+    pos_s[threadIdx.x] = positions[t];
   }
   __syncthreads();
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
     const float* w = conv_w + (size_t)c * K;
     const float bias = conv_b ? conv_b[c] : 0.f;
+    const float xb = in_bias ? in_bias[c] : 0.f;       // a bias of the projection itself: only real tokens carry it
     for (int i = 0; i < nt; ++i) {
       const int n_prev = n_prev_s[i], t = t0 + i;
       if (n_prev < 0) continue;
       const float* tail = state + (size_t)slot_s[i] * slot_stride + tail_offset;
-      float acc = bias + w[K - 1] * proj[(size_t)t * proj_stride + col0 + c];
+      float acc = bias + w[K - 1] * (proj[(size_t)t * proj_stride + col0 + c] + xb);
       for (int j = 1; j < K; ++j) {
-        const float x = j <= n_prev ? proj[(size_t)(t - j) * proj_stride + col0 + c]
-                                    : tail[(size_t)c * (K - 1) + (n_prev - j + K - 1)];
+        float x = j <= n_prev ? proj[(size_t)(t - j) * proj_stride + col0 + c]
+                              : tail[(size_t)c * (K - 1) + (n_prev - j + K - 1)];
+        if (pos_s[i] - j >= 0) x += xb;
         acc = fmaf(w[K - 1 - j], x, acc);
       }
-      out[(size_t)t * out_stride + c] = acc * sigmoid_f(acc);
+      out[(size_t)t * out_stride + c] = act ? acc * sigmoid_f(acc) : acc;
     }
   }
 }
@@ -94,6 +100,113 @@ __global__ void conv_tail_kernel(float* __restrict__ state, size_t slot_stride, 
       tc[m] = from_step >= 0 ? proj[(size_t)(start + from_step) * proj_stride + col0 + c] : tc[m + n];
     }
   }
+}
+
+// The gates of a gated linear recurrence over R = parts * size channels (the real-gated linear recurrent
+// unit of Griffin): with u the recurrence's input, cut into `parts` equal parts,
+//     r = sigmoid(W_a[p] u_p + b_a),  i = sigmoid(W_i[p] u_p + b_i)          (square matrices per part)
+//     log a = -rate * r * softplus(lam),  a = exp(log a),  x = sqrt(1 - a^2) * i * u
+// so that the recurrence itself is S_t = a_t S_(t-1) + x_t.  1 - a^2 is taken as -expm1(2 log a), which
+// keeps its digits when a is close to 1.  grid (token tiles of 16, parts, output tiles of 128); a block
+// stages its tokens' u_p in shared memory, a thread owns one output channel for all 16 tokens, and the
+// weights come transposed ([in][out]) so that neighbouring threads read neighbouring words.
+constexpr int kLruTokens = 16;
+__global__ void __launch_bounds__(128)
+lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ x_out, const float* __restrict__ u, int u_stride,
+                 const float* __restrict__ w_a, const float* __restrict__ b_a, const float* __restrict__ w_i,
+                 const float* __restrict__ b_i, const float* __restrict__ lam, float rate, int n_tokens, int parts,
+                 int size) {
+  extern __shared__ __align__(16) float u_s[];     // [kLruTokens][size]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t0 = blockIdx.x * kLruTokens, p = blockIdx.y, tid = threadIdx.x;
+  const int nt = min(kLruTokens, n_tokens - t0);
+  const int R = parts * size;
+  for (int idx = tid; idx < kLruTokens * size; idx += blockDim.x) {
+    const int tt = idx / size, r = idx % size;
+    u_s[idx] = tt < nt ? u[(size_t)(t0 + tt) * u_stride + p * size + r] : 0.f;
+  }
+  __syncthreads();
+  const int o = blockIdx.z * 128 + tid;
+  if (o >= size) return;
+  const int c = p * size + o;
+  float ra[kLruTokens], ri[kLruTokens];
+  const float ba = b_a ? b_a[c] : 0.f, bi = b_i ? b_i[c] : 0.f;
+#pragma unroll
+  for (int tt = 0; tt < kLruTokens; ++tt) { ra[tt] = ba; ri[tt] = bi; }
+  const float* wa = w_a + (size_t)p * size * size + o;
+  const float* wi = w_i + (size_t)p * size * size + o;
+  for (int r = 0; r < size; ++r) {
+    const float va = wa[(size_t)r * size], vi = wi[(size_t)r * size];
+#pragma unroll
+    for (int tt = 0; tt < kLruTokens; ++tt) {
+      const float x = u_s[tt * size + r];
+      ra[tt] = fmaf(va, x, ra[tt]);
+      ri[tt] = fmaf(vi, x, ri[tt]);
+    }
+  }
+  const float sp = rate * softplus_f(lam[c]);
+#pragma unroll
+  for (int tt = 0; tt < kLruTokens; ++tt) {
+    if (tt < nt) {
+      const float log_a = -sp * sigmoid_f(ra[tt]);
+      const size_t at = (size_t)(t0 + tt) * R + c;
+      a_out[at] = expf(log_a);
+      x_out[at] = sqrtf(-expm1f(2.f * log_a)) * sigmoid_f(ri[tt]) * u_s[tt * size + o];
+    }
+  }
+}
+
+// S_t = a_t S_(t-1) + x_t per channel and sequence, S read from and written back to the slot's state
+// (its first `channels` values, 32-bit); out[t, c] = S_t * gelu_tanh(side[t, side_col + c] + side_bias[c]),
+// rounded to the activation type.  grid (sequences, channel tiles of 128): a thread walks one channel's
+// tokens; only the multiply-add is on the chain, the loads of the tokens ahead are independent of it.
+template <typename T>
+__global__ void __launch_bounds__(128)
+lru_scan_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ x,
+                const float* __restrict__ side, int side_stride, int side_col, const float* __restrict__ side_bias,
+                float* __restrict__ state, size_t slot_stride, const int* __restrict__ cu_seqlens,
+                const int* __restrict__ positions, const int* __restrict__ token_slot, int channels,
+                int write_state) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x, c = blockIdx.y * 128 + threadIdx.x;
+  const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+  if (c >= channels || n <= 0) return;
+  if (positions[start] < 0) {                   // rows of a finished sequence: zeros, the state untouched
+    for (int i = 0; i < n; ++i) out[(size_t)(start + i) * channels + c] = from_f<T>(0.f);
+    return;
+  }
+  float* sp = state + (size_t)token_slot[start] * slot_stride + c;
+  float S = *sp;
+  const float sb = side_bias ? side_bias[c] : 0.f;
+  constexpr int U = 8;
+  int i = 0;
+  for (; i + U <= n; i += U) {
+    float av[U], xv[U], yv[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      const size_t row = (size_t)(start + i + j);
+      av[j] = a[row * channels + c];
+      xv[j] = x[row * channels + c];
+      yv[j] = side[row * side_stride + side_col + c] + sb;
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      S = fmaf(av[j], S, xv[j]);
+      const float z = yv[j];
+      const float g = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+      out[(size_t)(start + i + j) * channels + c] = from_f<T>(S * g);
+    }
+  }
+  for (; i < n; ++i) {
+    const size_t row = (size_t)(start + i);
+    S = fmaf(a[row * channels + c], S, x[row * channels + c]);
+    const float z = side[row * side_stride + side_col + c] + sb;
+    const float g = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    out[row * channels + c] = from_f<T>(S * g);
+  }
+  if (write_state) *sp = S;
 }
 
 // a[t, h] = exp(-exp(a_log[h]) dt), b[t, h] = dt, dt = softplus(proj[t, col0 + h] + dt_bias[h]).
@@ -433,8 +546,60 @@ EK_EXPORT int ek_conv_silu(float* out, int out_stride, const float* proj, int pr
   return (int)ek::launch_pdl(ek::conv_silu_kernel, dim3((n_tokens + per_block - 1) / per_block, tiles < 65535 ? tiles : 65535),
                              dim3(256), 0, stream, out, out_stride, proj, proj_stride, col0, conv_w, conv_b, state,
                              (size_t)slot_stride, (size_t)tail_offset, positions, token_slot, n_tokens, channels,
-                             taps, per_block);
+                             taps, per_block, (const float*)nullptr, 1);
 }
+
+// The same convolution with two options: `in_bias` [channels] is added to every input that belongs to a
+// token (the inputs before a sequence's start stay zero), and `act` 0 leaves the SiLU out.
+EK_EXPORT int ek_conv_act(float* out, int out_stride, const float* proj, int proj_stride, int col0,
+                          const float* conv_w, const float* conv_b, const float* in_bias, int act,
+                          const float* state, long long slot_stride, long long tail_offset, const int* positions,
+                          const int* token_slot, int n_tokens, int channels, int taps, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (channels <= 0 || taps < 1) return EK_ERR_ARG;
+  const int tiles = (channels + 255) / 256;
+  const int per_block = n_tokens >= 2048 ? ek::kConvTokens : n_tokens >= 256 ? 4 : 1;
+  return (int)ek::launch_pdl(ek::conv_silu_kernel, dim3((n_tokens + per_block - 1) / per_block, tiles < 65535 ? tiles : 65535),
+                             dim3(256), 0, stream, out, out_stride, proj, proj_stride, col0, conv_w, conv_b, state,
+                             (size_t)slot_stride, (size_t)tail_offset, positions, token_slot, n_tokens, channels,
+                             taps, per_block, in_bias, act);
+}
+
+// Both gates of the gated linear recurrence and what enters it: a[t, c] and x[t, c] (see lru_gates_kernel).
+// u [T, R] 32-bit rows `u_stride` apart; w_a, w_i [parts][in][out] (transposed at load); R = parts * size.
+EK_EXPORT int ek_lru_gates(float* a, float* x, const float* u, int u_stride, const float* w_a, const float* b_a,
+                           const float* w_i, const float* b_i, const float* lam, float rate, int n_tokens,
+                           int parts, int size, cudaStream_t stream) {
+  using namespace ek;
+  if (n_tokens <= 0) return 0;
+  if (parts <= 0 || size <= 0 || parts > 65535) return EK_ERR_ARG;
+  const size_t smem = (size_t)kLruTokens * size * sizeof(float);
+  if (smem > 200 * 1024) return EK_ERR_ARG;
+  if (smem > 40 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(lru_gates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid((n_tokens + kLruTokens - 1) / kLruTokens, parts, (size + 127) / 128);
+  return (int)launch_pdl(lru_gates_kernel, grid, dim3(128), smem, stream, a, x, u, u_stride, w_a, b_a, w_i, b_i, lam,
+                         rate, n_tokens, parts, size);
+}
+
+#define EK_LRU_SCAN(SUFFIX, T)                                                                              \
+  EK_EXPORT int ek_lru_scan_##SUFFIX(void* out, const float* a, const float* x, const float* side,            \
+                                     int side_stride, int side_col, const float* side_bias, float* state,    \
+                                     long long slot_stride, const int* cu_seqlens, const int* positions,     \
+                                     const int* token_slot, int n_seqs, int channels, int write_state,       \
+                                     cudaStream_t stream) {                                                  \
+    if (n_seqs <= 0) return 0;                                                                               \
+    if (channels <= 0) return EK_ERR_ARG;                                                                    \
+    dim3 grid(n_seqs, (channels + 127) / 128);                                                               \
+    if (grid.y > 65535) return EK_ERR_ARG;                                                                   \
+    return (int)ek::launch_pdl(ek::lru_scan_kernel<T>, grid, dim3(128), 0, stream, (T*)out, a, x, side,      \
+                               side_stride, side_col, side_bias, state, (size_t)slot_stride, cu_seqlens,     \
+                               positions, token_slot, channels, write_state);                                \
+  }
+EK_LRU_SCAN(f32, float)
+EK_LRU_SCAN(bf16, ek::bf16)
 
 EK_EXPORT int ek_conv_tail(float* state, long long slot_stride, long long tail_offset, const float* proj,
                            int proj_stride, int col0, const int* cu_seqlens, const int* positions,

@@ -19,6 +19,9 @@ constexpr int kRopeWarps = 4;
 // scores of late positions step by step; and values that are the keys as projected (bias added,
 // before the key norm and rotation): the row then has no value heads, and a key head is stored
 // twice, raw in the value pages and normalised in the key pages.
+// `norm_dim` > 0: heads are padded with zeros up to the cache's head size and the query / key norm takes
+// its mean over the first norm_dim values only.  `v_unit`: every value head is divided by its root mean
+// square over its first v_norm_dim values (eps v_eps, no gain) before it is stored.
 struct QkExtras {
   const float* q_bias;
   const float* k_bias;
@@ -26,6 +29,10 @@ struct QkExtras {
   float q_temp_coef;
   int q_temp_every;
   int v_from_k;
+  int norm_dim;
+  int v_unit;
+  int v_norm_dim;
+  float v_eps;
 };
 
 
@@ -68,6 +75,25 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
   // Four neighbouring dimensions a lane when the sizes allow (head size a multiple of 4 and
   // the rotated half a multiple of 4), else one.
   const bool vec = (d % 4 == 0) && (rot_dim % 8 == 0) && (row_stride % 4 == 0);
+  if (!is_q && !is_k && ex.v_unit) {          // values over their root mean square
+    float y[EK_MAX_HEAD_DIM / 32];
+    float ssv = 0.f;
+#pragma unroll
+    for (int r = 0; r < EK_MAX_HEAD_DIM / 32; ++r) {
+      const int i = lane + 32 * r;
+      float v = 0.f;
+      if (i < d) v = to_f<T>(src[i]) + (bias ? bias[i] : 0.f);
+      y[r] = v;
+      ssv += v * v;
+    }
+    const float rv = rsqrtf(warp_sum(ssv) / (float)(ex.v_norm_dim > 0 ? ex.v_norm_dim : d) + ex.v_eps);
+#pragma unroll
+    for (int r = 0; r < EK_MAX_HEAD_DIM / 32; ++r) {
+      const int i = lane + 32 * r;
+      if (i < d) dst[i] = from_f<T>(y[r] * rv);
+    }
+    return;
+  }
   if (!is_q && !is_k) {                       // values: a copy (plus the bias)
     if (vec) {
       for (int i = lane * 4; i < d; i += 128) {
@@ -103,7 +129,7 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
   float rstd = 1.f;
   if (gain) {
     ss = warp_sum(ss);
-    rstd = rsqrtf(ss / (float)d + eps);
+    rstd = rsqrtf(ss / (float)(ex.norm_dim > 0 ? ex.norm_dim : d) + eps);
   }
   if (is_q && ex.q_temp_coef != 0.f)          // the rotation is linear: the factor may come first
     rstd *= 1.f + ex.q_temp_coef * logf((float)((pos + 1) / ex.q_temp_every) + 1.f);
@@ -498,8 +524,9 @@ static int launch(void* qkv, int row_stride, const float* q_gain, const float* k
       (rot_dim & 1) || n_tokens > 2147483647 / 2 || (ex.q_temp_coef != 0.f && ex.q_temp_every <= 0))
     return EK_ERR_ARG;
   PagedKV cache{k_pages, v_pages, block_table, table_stride, n_kv_heads, head_dim};
-  const bool plain = !ex.q_bias && !ex.k_bias && !ex.v_bias && ex.q_temp_coef == 0.f && !ex.v_from_k;
-  if (!plain && rot_dim == 0 && sizeof(T) == 2 && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+  const bool padded = ex.norm_dim > 0 || ex.v_unit;      // only the warp-a-head kernel knows these
+  const bool plain = !ex.q_bias && !ex.k_bias && !ex.v_bias && ex.q_temp_coef == 0.f && !ex.v_from_k && !padded;
+  if (!plain && !padded && rot_dim == 0 && sizeof(T) == 2 && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
       n_tokens >= 128 && row_stride % 8 == 0) {
     auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     if (aligned(qkv) && aligned(q_gain) && aligned(k_gain) && aligned(k_pages) && aligned(v_pages) &&
@@ -558,7 +585,24 @@ static int launch(void* qkv, int row_stride, const float* q_gain, const float* k
       int n_q_heads, int n_kv_heads, int head_dim, float eps, int write_kv,                    \
       const float* q_bias, const float* k_bias, const float* v_bias, float q_temp_coef,        \
       int q_temp_every, int v_from_k, cudaStream_t stream) {                                   \
-    ek::QkExtras ex{q_bias, k_bias, v_bias, q_temp_coef, q_temp_every, v_from_k};              \
+    ek::QkExtras ex{q_bias, k_bias, v_bias, q_temp_coef, q_temp_every, v_from_k, 0, 0, 0, 0.f}; \
+    return ek::launch<T>(qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, positions, \
+                         token_slot, k_pages, v_pages, block_table, table_stride, n_tokens,    \
+                         n_q_heads, n_kv_heads, head_dim, eps, write_kv, ex, stream);          \
+  }                                                                                            \
+  /* The same for heads padded with zeros to the cache's head size: the gained query / key    */ \
+  /* norm takes its mean over norm_dim values, and with v_unit a value head is divided by its */ \
+  /* root mean square over v_norm_dim values before it is stored.                             */ \
+  EK_EXPORT int ek_qk_prepare_padded_kv_##SUFFIX(                                               \
+      void* qkv, int row_stride, const float* q_gain, const float* k_gain, const float* cos_tab, \
+      const float* sin_tab, int rot_dim, const int* positions, const int* token_slot,          \
+      void* k_pages, void* v_pages, const int* block_table, int table_stride, int n_tokens,    \
+      int n_q_heads, int n_kv_heads, int head_dim, float eps, int write_kv,                    \
+      const float* q_bias, const float* k_bias, const float* v_bias, int norm_dim, int v_unit, \
+      int v_norm_dim, float v_eps, cudaStream_t stream) {                                      \
+    if (norm_dim <= 0 || norm_dim > head_dim || (v_unit && (v_norm_dim <= 0 || v_norm_dim > head_dim))) \
+      return EK_ERR_ARG;                                                                       \
+    ek::QkExtras ex{q_bias, k_bias, v_bias, 0.f, 1, 0, norm_dim, v_unit, v_norm_dim, v_eps};   \
     return ek::launch<T>(qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, positions, \
                          token_slot, k_pages, v_pages, block_table, table_stride, n_tokens,    \
                          n_q_heads, n_kv_heads, head_dim, eps, write_kv, ex, stream);          \

@@ -34,6 +34,10 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
         out[spec.lm_head.name] = spec.lm_head
     if spec.position_table is not None:
         out[spec.position_table.name] = spec.position_table
+    if spec.pair_table is not None:
+        out[spec.pair_table.table.name] = spec.pair_table.table
+    if spec.input_mix is not None:
+        out[spec.input_mix.name] = spec.input_mix
     for ts in _part_tensors("norm", spec.final_norm):
         out[ts.name] = ts
     for layer in spec.layers:
@@ -73,7 +77,7 @@ class DecoderModel:
             norms = {n: lookup_part("norm", s.kind)(s, dtype, device) for n, s in layer.norms.items()}
             self.blocks.append(block_cls(layer.block, dtype, device, mixer, ff, norms))
         self.final_norm = lookup_part("norm", spec.final_norm.kind)(spec.final_norm, dtype, device)
-        self.embedding = self.lm_head = self.position_table = None
+        self.embedding = self.lm_head = self.position_table = self.pair_table = self.input_mix = None
         self._prepared_for = 0
 
     # -- weights ---------------------------------------------------------------
@@ -87,6 +91,10 @@ class DecoderModel:
             self.lm_head = tensors[s.lm_head.name].to(self.dtype).contiguous()
         if s.position_table is not None:
             self.position_table = tensors[s.position_table.name].to(self.dtype).contiguous()
+        if s.pair_table is not None:
+            self.pair_table = tensors[s.pair_table.table.name].to(self.dtype).contiguous()
+        if s.input_mix is not None:
+            self.input_mix = tensors[s.input_mix.name].to(self.dtype).contiguous()
         self.final_norm.load(tensors)
         for block in self.blocks:
             block.load(tensors)
@@ -116,6 +124,15 @@ class DecoderModel:
                     and specs[run.cache].group_key() != cs.group_key():
                 raise ValueError(f"cache entry {run.cache} is shared by mixers with different needs")
             specs[run.cache] = cs if cs is not None else specs[run.cache]
+            more = self.blocks[run.layer].mixer.extra_cache_specs()
+            if len(more) != len(run.more_caches):
+                raise ValueError(f"layer {run.layer}'s mixer keeps {len(more)} further cache entries, "
+                                 f"its run names {len(run.more_caches)}")
+            for c, cs in zip(run.more_caches, more):
+                specs[c] = cs
+        if self.spec.pair_table is not None:
+            # the token before the next one, per sequence
+            specs[self.spec.pair_table.cache] = CacheSpec("state", shape=(1,), state_dtype="int32")
         return specs
 
     def weight_bytes_read_per_step(self, n_tokens: int = 1) -> int:
@@ -124,6 +141,9 @@ class DecoderModel:
         LM head.  Embedding rows are left out (a few rows of the table)."""
         total = self.lm_head.numel() * self.lm_head.element_size()
         total += self.final_norm.bytes_read_per_step(n_tokens)
+        if self.input_mix is not None:
+            total += sum(1 for run in self.spec.schedule if run.mix_input) * \
+                self.input_mix.numel() * self.input_mix.element_size()
         for run in self.spec.schedule:
             b = self.blocks[run.layer]
             for part in (b, b.mixer, b.feed_forward, *b.norms.values()):
@@ -141,6 +161,21 @@ class DecoderModel:
         stream = ctx.workspace.get("stream", (t, self.spec.hidden_size), torch.float32)
         kernels.embed(stream, self.embedding, ctx.token_ids, t, scale=self.spec.embedding_multiplier,
                       pos_table=self.position_table, positions=ctx.positions)
+        pairs = self.spec.pair_table
+        if pairs is not None:
+            # the row of the hashed pair table that (previous token, token) names joins the embedding;
+            # the token before a step's first one of a sequence is read from the sequence's state,
+            # and afterwards (a launch of its own, so that no read meets it) the state gets the last
+            before = cache.entry(pairs.cache).state
+            kernels.embed_pair(stream, self.pair_table, ctx.token_ids, ctx.positions, ctx.token_slot, before, t,
+                               pairs.buckets, pairs.mul_prev, pairs.mul_cur)
+            kernels.keep_last_token(before, ctx.token_ids, ctx.positions, ctx.token_slot, t)
+        joined = None
+        if self.input_mix is not None:
+            # [x ; x0] as the operand of the input mix: the right half is the embedding output for the
+            # whole step, the left half is filled in before every pass
+            joined = ctx.workspace.get("input_mix_operand", (t, 2 * self.spec.hidden_size), self.dtype)
+            kernels.cast_columns(joined, self.spec.hidden_size, stream, t)
         pending = None
         schedule = self.spec.schedule
         stream = self.blocks[schedule[0].layer].open_stream(stream, ctx)
@@ -151,13 +186,26 @@ class DecoderModel:
                 # stream again (the pending output of the block before is added by the next norm)
                 kernels.embed(stream, self.embedding, ctx.token_ids, t, scale=self.spec.embedding_multiplier,
                               pos_table=self.position_table, positions=ctx.positions, accumulate=True)
+            if run.mix_input:
+                # x <- W [x ; x0]: what is still to be added joins the stream first, the product's
+                # 32-bit result is the new stream
+                stream, pending = self.blocks[schedule[i - 1].layer].collapse(stream, pending, ctx) if i > 0 \
+                    else (stream, pending)
+                if pending is not None:
+                    kernels.add_residual(stream, pending, n_rows=t)
+                    pending = None
+                kernels.cast_columns(joined, 0, stream, t)
+                stream = linear(joined, self.input_mix, ctx, "stream_mixed", n_rows=t, out_dtype=torch.float32,
+                                wide_f32="library")
             entry = cache.entry(run.cache) if run.cache is not None and \
                 block.mixer.cache_spec() is not None else None
+            if run.more_caches:
+                entry = [entry] + [cache.entry(c) for c in run.more_caches]
             # a block that can leave its last add and the next norm to its own last product is told
             # which norm comes next (none after the last block: the final norm picks rows)
             # (and none when the embedding output is added in between: the norm would miss it)
             follower = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) and \
-                not schedule[i + 1].add_embedding else None
+                not schedule[i + 1].add_embedding and not schedule[i + 1].mix_input else None
             next_norm = getattr(follower, "first_norm", lambda: None)() if follower is not None else None
             if next_norm is not None:
                 pending = block.forward(stream, pending, ctx, entry, run.writes_cache, next_norm=next_norm)

@@ -1,2 +1,2 @@
 """Architectures: each module registers its name, configuration class and builder."""
-from . import bolelix, lopazen, qwen3, susalorn  # noqa: F401
+from . import bolelix, lopazen, musavik, qwen3, susalorn  # noqa: F401

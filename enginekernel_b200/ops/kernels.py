@@ -232,6 +232,88 @@ def act_mul(out, gu, activation="silu", n_rows=None):
                            _stream())
 
 
+_embed_pair = _per_dtype("elementwise", "ek_embed_pair",
+                         [_P, _P, _P, _P, _P, _P, c_longlong, c_int, c_int, c_int, c_longlong, c_longlong, _P])
+_keep_last_token = Function("elementwise", "ek_keep_last_token", [_P, c_longlong, _P, _P, _P, c_int, _P])
+_cast_columns = _per_dtype("elementwise", "ek_cast_columns", [_P, c_int, c_int, _P, c_int, c_int, _P])
+_rmsnorm_post_add = _per_dtype("elementwise", "ek_rmsnorm_post_add",
+                               [_P, _P, _P, c_float, _P, c_float, _P, _P, c_float, _P, c_float, c_int, c_int, _P])
+_bias_act = _per_dtype("elementwise", "ek_bias_act", [_P, _P, c_int, c_int, c_int, _P, c_int, c_int, c_int, _P])
+ROW_ACTIVATIONS = {None: 0, "none": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def embed_pair(resid, table, ids, positions, token_slot, before, n_tokens, buckets, mul_prev, mul_cur):
+    """resid[t] += table[(previous * mul_prev + ids[t] * mul_cur) mod buckets], and table[buckets] for a
+    sequence's first token (position 0).  The token before t is the step's token t - 1 when that continues
+    the same sequence, else ``before[slot]`` (int32, one per slot).  Rows with a negative position are skipped."""
+    _need_cuda(resid, table, ids, positions, token_slot, before)
+    hidden = resid.shape[-1]
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and table.is_contiguous()
+          and tuple(table.shape) == (buckets + 1, hidden), "embed_pair: 32-bit stream, table [buckets + 1, hidden]")
+    _need(before.dtype == torch.int32 and ids.dtype == torch.int32 and positions.dtype == torch.int32
+          and token_slot.dtype == torch.int32, "embed_pair: int32 indices and previous tokens")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * hidden * (table.element_size() + 8))
+    _embed_pair[table.dtype](_ptr(resid), _ptr(table), _ptr(ids), _ptr(positions), _ptr(token_slot), _ptr(before),
+                             before.stride(0), n_tokens, hidden, int(buckets), int(mul_prev), int(mul_cur), _stream())
+
+
+def keep_last_token(before, ids, positions, token_slot, n_tokens):
+    """before[slot] = the last token each sequence of the step brought."""
+    _need_cuda(before, ids, positions, token_slot)
+    _need(before.dtype == torch.int32, "keep_last_token: int32 state")
+    _keep_last_token(_ptr(before), before.stride(0), _ptr(ids), _ptr(positions), _ptr(token_slot), n_tokens, _stream())
+
+
+def cast_columns(dst, col0, src, n_rows):
+    """dst[r, col0 : col0 + W] = src[r, :] (32-bit, [rows, W]) rounded to dst's type."""
+    _need_cuda(dst, src)
+    width = src.shape[-1]
+    _need(src.dtype == torch.float32 and src.is_contiguous() and dst.stride(-1) == 1
+          and col0 + width <= dst.shape[-1], "cast_columns: 32-bit source rows that fit the destination's")
+    if lib.recording():
+        lib.annotate(bytes=n_rows * width * (4 + dst.element_size()))
+    _cast_columns[dst.dtype](_ptr(dst), dst.stride(0), col0, _ptr(src), width, n_rows, _stream())
+
+
+def rmsnorm_post_add(y, resid, a, gain_post, eps_post, gain=None, eps=0.0, weight_a=1.0, b=None, weight_b=1.0,
+                     bias=None, n_rows=None):
+    """stream += gain_post * n(u), u = a * weight_a + b * weight_b + bias (``b``, ``bias`` optional; the
+    weights are plain numbers), and then, when ``y`` is given, y = gain * n(stream): a sublayer's result
+    normed on its way into the stream and the next reader's norm, one pass over the row."""
+    _need_cuda(y, resid, a, gain_post, gain, b, bias)
+    hidden = resid.shape[-1]
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and gain_post.dtype == torch.float32
+          and gain_post.numel() == hidden, "rmsnorm_post_add: 32-bit stream and gains of its width")
+    _need(a.is_contiguous() and a.shape[-1] == hidden and (b is None or (b.dtype == a.dtype and b.is_contiguous()
+          and b.shape[-1] == hidden)), "rmsnorm_post_add: results of the stream's width")
+    _need(y is None or (y.dtype == a.dtype and y.is_contiguous() and y.shape[-1] == hidden and gain is not None
+                        and gain.dtype == torch.float32 and gain.numel() == hidden),
+          "rmsnorm_post_add: y in the results' type with a 32-bit gain")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == hidden), "rmsnorm_post_add: 32-bit bias")
+    n = n_rows if n_rows is not None else resid.shape[0]
+    if lib.recording():
+        lib.annotate(bytes=n * hidden * (8 + a.element_size() * ((1 if b is None else 2) + (0 if y is None else 1))))
+    _rmsnorm_post_add[a.dtype](_ptr(y), _ptr(resid), _ptr(a), float(weight_a), _ptr(b), float(weight_b), _ptr(bias),
+                               _ptr(gain_post), float(eps_post), _ptr(gain), float(eps), n, hidden, _stream())
+
+
+def bias_act(out, x, bias=None, activation=None, col0=0, n_rows=None):
+    """out[r, i] = act(x[r, col0 + i] + bias[i]) over out's width; ``x`` is 32-bit or of out's type;
+    ``activation`` None, ``"gelu_tanh"`` or ``"silu"``."""
+    _need_cuda(out, x, bias)
+    _need(activation in ROW_ACTIVATIONS, f"bias_act: no activation {activation!r}")
+    width = out.shape[-1]
+    _need(out.is_contiguous() and x.stride(-1) == 1 and x.dtype in (torch.float32, out.dtype)
+          and col0 + width <= x.shape[-1], "bias_act: rows of out's width inside x's rows")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == width), "bias_act: a 32-bit bias of out's width")
+    n = n_rows if n_rows is not None else out.shape[0]
+    if lib.recording():
+        lib.annotate(bytes=n * width * (x.element_size() + out.element_size()))
+    _bias_act[out.dtype](_ptr(out), _ptr(x), 1 if x.dtype == torch.float32 else 0, x.stride(0), col0, _ptr(bias),
+                         width, n, ROW_ACTIVATIONS[activation], _stream())
+
+
 # ------------------------------------------------------------------ rope + cache write
 _rope_kv = _per_dtype("rope_kv", "ek_qk_norm_rope_kv",
                       [_P, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int,
@@ -282,6 +364,40 @@ def qk_prepare_kv(qkv, n_tokens, q_gain, k_gain, cos, sin, rot_dim, positions, t
                            _ptr(block_table), block_table.stride(0), n_tokens, n_q_heads, n_kv_heads,
                            head_dim, float(eps), 1 if write_kv else 0, _ptr(q_bias), _ptr(k_bias),
                            _ptr(v_bias), coef, every, 1 if values_from_keys else 0, _stream())
+
+
+_qk_prepare_padded = _per_dtype("rope_kv", "ek_qk_prepare_padded_kv",
+                                [_P, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int,
+                                 c_int, c_int, c_float, c_int, _P, _P, _P, c_int, c_int, c_int, c_float, _P])
+
+
+def qk_prepare_padded_kv(qkv, n_tokens, q_gain, k_gain, cos, sin, rot_dim, positions, token_slot,
+                         k_pages, v_pages, block_table, n_q_heads, n_kv_heads, head_dim, eps, norm_dim,
+                         write_kv=True, q_bias=None, k_bias=None, v_bias=None, value_unit_eps=None,
+                         value_dim=None):
+    """:func:`qk_prepare_kv` for heads padded with zeros to ``head_dim`` (the cache's head size): the
+    gained norm of queries and keys takes its mean over ``norm_dim`` values; with ``value_unit_eps`` every
+    value head is divided by its root mean square over ``value_dim`` values before it is stored."""
+    _need_cuda(qkv, cos, sin, positions, token_slot, k_pages, v_pages, block_table, q_bias, k_bias, v_bias)
+    check_head_dim(head_dim)
+    heads = n_q_heads + 2 * n_kv_heads
+    _need(qkv.stride(-1) == 1 and qkv.shape[-1] >= heads * head_dim, "qk_prepare_padded_kv: row width")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+          and cos.shape[-1] * 2 == rot_dim, "qk_prepare_padded_kv: 32-bit tables of rot_dim/2 columns")
+    _need(k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype, "qk_prepare_padded_kv: cache dtype")
+    for g in (q_gain, k_gain):
+        _need(g is None or (g.dtype == torch.float32 and g.numel() == head_dim), "qk gains: 32-bit [D]")
+    for b, n in ((q_bias, n_q_heads), (k_bias, n_kv_heads), (v_bias, n_kv_heads)):
+        _need(b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == n * head_dim),
+              "qk_prepare_padded_kv: biases are 32-bit [heads * D]")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * head_dim * qkv.element_size() * (2 * n_q_heads + 3 * n_kv_heads))
+    _qk_prepare_padded[qkv.dtype](_ptr(qkv), qkv.stride(0), _ptr(q_gain), _ptr(k_gain), _ptr(cos), _ptr(sin),
+                                  rot_dim, _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages),
+                                  _ptr(block_table), block_table.stride(0), n_tokens, n_q_heads, n_kv_heads,
+                                  head_dim, float(eps), 1 if write_kv else 0, _ptr(q_bias), _ptr(k_bias),
+                                  _ptr(v_bias), int(norm_dim), 1 if value_unit_eps is not None else 0,
+                                  int(value_dim or head_dim), float(value_unit_eps or 0.0), _stream())
 
 
 def qk_norm_rope_kv(qkv, n_tokens, q_gain, k_gain, cos, sin, rot_dim, positions, token_slot,
@@ -395,6 +511,55 @@ def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages,
                            _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
     if n_splits > 1:
         count_extra_launches()               # the merge kernel
+
+
+_attn_generic_cross = _per_dtype("attention_generic", "ek_attention_generic_cross",
+                                 [_P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                                  c_float, c_int, c_int, c_int, _P, _P, c_int, _P])
+_mix_heads = _per_dtype("attention_generic", "ek_mix_heads",
+                        [_P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P])
+
+
+def attention_generic_cross(parts, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table, n_q_heads,
+                            n_kv_heads, head_dim, scale, window=None, n_splits=1, keys_per_split=0, part_acc=None,
+                            part_ml=None, keep_first=0):
+    """parts[t, g, c, :] = softmax_g(scale q_g.K^T) V_c: every query head's weights (against its own key
+    head) applied to the values of EVERY key/value head c, in 32-bit ([T, NQ, NKV, D]) - what designs need
+    that mix the heads' weights behind the softmax (:func:`mix_heads`).  Split buffers as in
+    :func:`attention_generic`, with NQ * NKV rows a token."""
+    _need_cuda(parts, q, positions, token_slot, k_pages, v_pages, block_table, part_acc, part_ml)
+    _need(1 <= head_dim <= GENERIC_MAX_HEAD_DIM, f"attention_generic_cross: head sizes up to {GENERIC_MAX_HEAD_DIM}")
+    _need(q.dtype == k_pages.dtype and parts.dtype == torch.float32 and parts.is_contiguous()
+          and parts.numel() >= n_tokens * n_q_heads * n_kv_heads * head_dim and q.stride(-1) == 1,
+          "attention_generic_cross: parts [T, NQ, NKV, D] in 32-bit")
+    if n_splits > 1:
+        _need(part_acc is not None and part_ml is not None
+              and part_acc.numel() >= n_tokens * n_q_heads * n_kv_heads * n_splits * head_dim
+              and part_ml.numel() >= n_tokens * n_q_heads * n_kv_heads * n_splits * 2, "attention: split buffers")
+    _attention_cost(q, n_tokens, positions, n_q_heads * n_kv_heads, n_kv_heads, head_dim, window, False)
+    _attn_generic_cross[q.dtype](_ptr(parts), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
+                                 _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
+                                 n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
+                                 n_splits, keys_per_split, _ptr(part_acc), _ptr(part_ml), int(keep_first or 0),
+                                 _stream())
+    if n_splits > 1:
+        count_extra_launches()
+
+
+def mix_heads(out, parts, mix, positions, n_tokens, n_q_heads, n_kv_heads, head_dim, value_dim, gate=None):
+    """out[t, h, :] = sigmoid(gate[t, h, :]) * sum_g mix[h, g] parts[t, g, h // (NQ / NKV), :value_dim]
+    (``gate`` optional, rows of at least NQ * value_dim values in out's type; ``mix`` [NQ, NQ] 32-bit)."""
+    _need_cuda(out, parts, mix, positions, gate)
+    _need(parts.dtype == torch.float32 and mix.dtype == torch.float32 and mix.is_contiguous()
+          and mix.numel() == n_q_heads * n_q_heads and out.is_contiguous()
+          and out.shape[-1] == n_q_heads * value_dim, "mix_heads: out [T, NQ * value_dim], mix [NQ, NQ]")
+    _need(gate is None or (gate.dtype == out.dtype and gate.stride(-1) == 1
+                           and gate.shape[-1] >= n_q_heads * value_dim), "mix_heads: gate rows in out's type")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * n_q_heads * (4 * n_kv_heads * head_dim + 2 * value_dim * out.element_size()),
+                     flops=2 * n_tokens * n_q_heads * n_q_heads * value_dim)
+    _mix_heads[out.dtype](_ptr(out), _ptr(parts), _ptr(mix), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                          _ptr(positions), n_tokens, n_q_heads, n_kv_heads, head_dim, value_dim, _stream())
 
 
 _attn_decode_bf16 = Function("attention_decode_bf16", "ek_attention_decode_bf16",
@@ -1186,10 +1351,11 @@ _delta_low_rank = Function("delta", "ek_delta_low_rank",
 _delta_conv_tail = Function("delta", "ek_delta_conv_tail",
                             [_P, c_longlong, c_longlong, _P, c_int, _P, _P, _P, c_int, c_int, c_int, _P])
 _delta_scan = Function("delta", "ek_delta_scan",
-                       [_P, _P, _P, _P, _P, _P, _P, c_longlong, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P])
+                       [_P, _P, _P, _P, _P, _P, _P, c_longlong, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
+                        _P])
 _delta_out_norm = _per_dtype("delta", "ek_delta_out_norm",
                              [_P, _P, _P, _P, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_int, c_int, _P])
+                              c_int, c_int, c_int, c_int, _P])
 DELTA_MAX_KEY_DIM = 256
 
 
@@ -1240,28 +1406,34 @@ def delta_conv_tail(state, tail_offset, proj, cu_seqlens, positions, token_slot,
 
 
 def delta_scan(out, qn, kn, vc, beta, decay, state, cu_seqlens, positions, token_slot, n_seqs, heads,
-               kv_heads, dim, vdim, n_tokens=0):
+               kv_heads, dim, vdim, n_tokens=0, decay_per_head=False):
     """The recurrence over every sequence's tokens; S [heads, vdim, rows] at the start of a slot's state
-    is read and written back."""
+    is read and written back.  ``decay`` is [T, heads * dim] (one per key channel) or, with
+    ``decay_per_head``, [T, heads]."""
     _need_cuda(out, qn, kn, vc, beta, decay, state, cu_seqlens, positions, token_slot)
+    _need(decay.is_contiguous() and decay.shape[-1] == (heads if decay_per_head else heads * dim),
+          "delta_scan: decays [T, heads * dim], or [T, heads] with decay_per_head")
     if lib.recording():
         lib.annotate(bytes=4 * (n_tokens * (2 * kv_heads * dim + heads * dim + 2 * heads * vdim + heads)
                                 + 2 * n_seqs * heads * vdim * delta_state_rows(dim)),
                      flops=6 * n_tokens * heads * dim * vdim)
     _delta_scan(_ptr(out), _ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(decay), _ptr(state), state.stride(0),
                 _ptr(cu_seqlens), _ptr(positions), _ptr(token_slot), n_seqs, heads, kv_heads, dim, vdim,
-                _stream())
+                1 if decay_per_head else 0, _stream())
 
 
-def delta_out_norm(y, o, gate, w, eps, positions, n_tokens, shape):
-    """y = o / rms(o) per head * w * gate in the activation type (``o``, ``gate`` [T, heads * vdim] 32-bit)."""
+def delta_out_norm(y, o, gate, w, eps, positions, n_tokens, shape, gate_activation=None):
+    """y = o / rms(o) per head * w * gate in the activation type (``o`` [T, heads * vdim], ``gate`` rows of at
+    least as many values, 32-bit).  ``gate_activation="silu"``: the gate is a raw projection and its SiLU is taken here."""
     _need_cuda(y, o, gate, w, positions)
+    _need(gate_activation in (None, "silu"), "delta_out_norm: the gate is finished or takes SiLU")
     _need(o.dtype == gate.dtype == w.dtype == torch.float32 and y.is_contiguous() and o.is_contiguous()
-          and gate.is_contiguous(), "delta_out_norm: 32-bit inputs")
+          and gate.stride(-1) == 1, "delta_out_norm: 32-bit inputs")
     if lib.recording():
         lib.annotate(bytes=n_tokens * o.shape[-1] * (8 + y.element_size()))
     _delta_out_norm[y.dtype](_ptr(y), _ptr(o), _ptr(gate), _ptr(w), float(eps),
-                             _ptr(positions), n_tokens, *[int(v) for v in shape], _stream())
+                             _ptr(positions), n_tokens, *[int(v) for v in shape], gate.stride(0),
+                             1 if gate_activation == "silu" else 0, _stream())
 
 
 # ------------------------------------------------------------------ linear recurrences with a decay per head
@@ -1311,6 +1483,64 @@ def conv_silu(out, proj, col0, conv_w, conv_b, state, tail_offset, positions, to
         lib.annotate(bytes=8 * n_tokens * channels)
     _conv_silu(_ptr(out), out.stride(0), _ptr(proj), proj.stride(0), col0, _ptr(conv_w), _ptr(conv_b), _ptr(state),
                state.stride(0), tail_offset, _ptr(positions), _ptr(token_slot), n_tokens, channels, taps, _stream())
+
+
+_conv_act = Function("recurrent", "ek_conv_act",
+                     [_P, c_int, _P, c_int, c_int, _P, _P, _P, c_int, _P, c_longlong, c_longlong, _P, _P, c_int, c_int,
+                      c_int, _P])
+_lru_gates = Function("recurrent", "ek_lru_gates",
+                      [_P, _P, _P, c_int, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, _P])
+_lru_scan = _per_dtype("recurrent", "ek_lru_scan",
+                       [_P, _P, _P, _P, c_int, c_int, _P, _P, c_longlong, _P, _P, _P, c_int, c_int, c_int, _P])
+
+
+def conv_act(out, proj, col0, conv_w, conv_b, state, tail_offset, positions, token_slot, n_tokens, channels, taps,
+             in_bias=None, activation="silu"):
+    """:func:`conv_silu` with two options: ``in_bias`` [channels] is a bias of the projection itself, added
+    to every input that belongs to a token (what lies before a sequence's start stays zero; the state's
+    tail keeps the inputs without it); ``activation`` None leaves the SiLU out."""
+    _need_cuda(out, proj, conv_w, conv_b, in_bias, state, positions, token_slot)
+    _need_f32("conv_act", out, proj, conv_w, conv_b, in_bias, state)
+    _need(activation in (None, "silu"), "conv_act: SiLU or nothing")
+    _need(conv_w.is_contiguous() and tuple(conv_w.shape) == (channels, taps) and out.shape[-1] >= channels
+          and col0 + channels <= proj.shape[-1], "conv_act: weights [channels, taps], columns within the rows")
+    if lib.recording():
+        lib.annotate(bytes=8 * n_tokens * channels)
+    _conv_act(_ptr(out), out.stride(0), _ptr(proj), proj.stride(0), col0, _ptr(conv_w), _ptr(conv_b), _ptr(in_bias),
+              1 if activation == "silu" else 0, _ptr(state), state.stride(0), tail_offset, _ptr(positions),
+              _ptr(token_slot), n_tokens, channels, taps, _stream())
+
+
+def lru_gates(a, x, u, w_a, b_a, w_i, b_i, lam, rate, n_tokens, parts, size):
+    """Gates of a gated linear recurrence over ``parts * size`` channels: r = sigmoid(W_a[p] u_p + b_a),
+    i = sigmoid(W_i[p] u_p + b_i) per part p; a = exp(-rate * r * softplus(lam)), x = sqrt(1 - a^2) * i * u.
+    ``w_a``, ``w_i`` [parts, in, out] (transposed), everything 32-bit."""
+    _need_cuda(a, x, u, w_a, b_a, w_i, b_i, lam)
+    _need_f32("lru_gates", a, x, u, w_a, b_a, w_i, b_i, lam)
+    width = parts * size
+    _need(a.is_contiguous() and x.is_contiguous() and a.shape[-1] == width == x.shape[-1] and u.shape[-1] >= width
+          and w_a.is_contiguous() and w_i.is_contiguous() and tuple(w_a.shape) == (parts, size, size) == tuple(w_i.shape)
+          and lam.numel() == width, "lru_gates: a, x [T, parts * size]; weights [parts, size, size]")
+    if lib.recording():
+        lib.annotate(bytes=4 * (3 * n_tokens * width + 2 * parts * size * size), flops=4 * n_tokens * width * size)
+    _lru_gates(_ptr(a), _ptr(x), _ptr(u), u.stride(0), _ptr(w_a), _ptr(b_a), _ptr(w_i), _ptr(b_i), _ptr(lam),
+               float(rate), n_tokens, parts, size, _stream())
+
+
+def lru_scan(out, a, x, side, side_col, side_bias, state, cu_seqlens, positions, token_slot, n_seqs, channels,
+             write_state=True, n_tokens=0):
+    """S_t = a_t S_(t-1) + x_t per channel over every sequence's tokens, S (the first ``channels`` values of a
+    slot's state) read and written back; out[t, c] = S_t * gelu_tanh(side[t, side_col + c] + side_bias[c])."""
+    _need_cuda(out, a, x, side, side_bias, state, cu_seqlens, positions, token_slot)
+    _need_f32("lru_scan", a, x, side, side_bias, state)
+    _need(out.is_contiguous() and a.is_contiguous() and x.is_contiguous() and out.shape[-1] == channels
+          and a.shape[-1] == channels and side_col + channels <= side.shape[-1] and state.shape[-1] >= channels,
+          "lru_scan: out, a, x [T, channels]")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * channels * (12 + out.element_size()) + 8 * n_seqs * channels)
+    _lru_scan[out.dtype](_ptr(out), _ptr(a), _ptr(x), _ptr(side), side.stride(0), side_col, _ptr(side_bias),
+                         _ptr(state), state.stride(0), _ptr(cu_seqlens), _ptr(positions), _ptr(token_slot), n_seqs,
+                         channels, 1 if write_state else 0, _stream())
 
 
 def conv_tail(state, tail_offset, proj, col0, cu_seqlens, positions, token_slot, n_seqs, channels, taps):

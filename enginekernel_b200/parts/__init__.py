@@ -1,5 +1,6 @@
 """Parts a layer is put together from; importing this package registers the built-in kinds."""
-from . import attention, block, delta, hyper, latent_attention, mlp, moe, norm, recurrent, rope  # noqa: F401
+from . import (attention, block, delta, hyper, latent_attention, mixed_attention, mlp, moe, norm, pair,  # noqa: F401
+               recurrent, rope)
 from .base import Block, FeedForward, Mixer, Norm, Part, PositionEncoding, StepContext, Workspace
 from .spec import CacheSpec, LayerSpec, ModelSpec, PartSpec, RunSpec, TensorSpec
 

@@ -108,6 +108,16 @@ class DeferredNorm:
     eps: float
 
 
+class WeightedPair:
+    """What a mixer made of two mixers side by side leaves to whoever consumes its result:
+    a * weight_a + b * weight_b with two plain numbers.  The consumer (a block's norm kernel) forms the
+    sum on its way through the row, so that it costs no pass of its own."""
+    __slots__ = ("a", "weight_a", "b", "weight_b")
+
+    def __init__(self, a, weight_a, b, weight_b):
+        self.a, self.weight_a, self.b, self.weight_b = a, float(weight_a), b, float(weight_b)
+
+
 class Part:
     """Base of all parts."""
     role = ""
@@ -171,6 +181,12 @@ class Mixer(Part):
     def cache_spec(self) -> Optional[CacheSpec]:
         """What one cache entry of this mixer holds per sequence (None: nothing)."""
         return None
+
+    def extra_cache_specs(self) -> List[CacheSpec]:
+        """Further cache entries of a mixer that keeps more than one thing per sequence (the run names them
+        in ``RunSpec.more_caches``); ``forward`` then gets a list of entry views: the first for
+        :meth:`cache_spec`, the others in this order."""
+        return []
 
     def prepare(self, max_positions: int) -> None:
         """Called once the longest position is known (tables and the like)."""

@@ -1,5 +1,6 @@
-"""Pre-norm residual block: stream += mixer(norm(stream)); stream += ff(norm(stream)).
-A layer without a feed-forward is the first half alone (and needs only ``pre_mixer``).
+"""Block arrangements.  ``pre_norm``: stream += mixer(norm(stream)); stream += ff(norm(stream)).
+A layer without a feed-forward is the first half alone (and needs only ``pre_mixer``).  ``parallel``: one norm,
+two readers.  ``sandwich``: a norm before and behind each sublayer.
 
 The add of a part's output is folded into the norm that follows it, so a block takes the
 previous block's not-yet-added output (``pending``) and returns its own
@@ -12,7 +13,7 @@ import torch
 
 from ..ops import kernels
 from ..registry import register_part
-from .base import Block, DeferredNorm
+from .base import Block, DeferredNorm, WeightedPair
 from .spec import TensorSpec
 
 
@@ -123,3 +124,77 @@ class ParallelBlock(Block):
         a = self.mixer.forward(u, ctx, entry, writes_cache)
         b = self.feed_forward.forward(u, ctx) if self.feed_forward is not None else None
         return ScaledSum(a, self.scale_mixer, b, self.scale_ff)
+
+
+class PostNormed:
+    """What a ``sandwich`` block leaves to be added to the stream: gain * n(a * weight_a + b * weight_b + bias),
+    the norm being the sublayer's own second norm (``norm``; ``b`` and ``bias`` may be absent)."""
+    __slots__ = ("a", "weight_a", "b", "weight_b", "bias", "norm")
+
+    def __init__(self, result, norm, bias=None):
+        if isinstance(result, WeightedPair):
+            self.a, self.weight_a, self.b, self.weight_b = result.a, result.weight_a, result.b, result.weight_b
+        else:
+            self.a, self.weight_a, self.b, self.weight_b = result, 1.0, None, 1.0
+        self.bias, self.norm = bias, norm
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Block):
+    """A norm before and a norm behind every sublayer: stream += post_mixer(mixer(pre_mixer(stream))), then
+    stream += post_feed_forward(ff(pre_feed_forward(stream))).  A layer without a feed-forward is the
+    first half alone.  The norm behind a sublayer, the add and the norm before the next sublayer are one
+    kernel over the row (``rmsnorm_post_add``); the last block of a model, or a block before something
+    else reads the stream, does the norm and the add in ``collapse``.  All norms must be of the form
+    gain * x * rsqrt(mean(x^2) + eps).  A mixer may return a :class:`~.base.WeightedPair`, and a
+    feed-forward that can leave its last bias to the consumer (``forward(..., leave_bias=True)`` and
+    ``output_bias``) is asked to.  Norms: ``pre_mixer``, ``post_mixer``, ``pre_feed_forward``,
+    ``post_feed_forward``."""
+
+    @classmethod
+    def norm_names(cls, spec):
+        return ["pre_mixer", "post_mixer"]          # and the two of the feed-forward when there is one
+
+    def __init__(self, spec, dtype, device, mixer, feed_forward, norms):
+        super().__init__(spec, dtype, device, mixer, feed_forward, norms)
+        needed = ["pre_mixer", "post_mixer"] + (["pre_feed_forward", "post_feed_forward"] if feed_forward is not None else [])
+        for n in needed:
+            if n not in norms:
+                raise ValueError(f"block 'sandwich' needs the norm {n!r}")
+            if norms[n].deferrable() is None:
+                raise ValueError("block 'sandwich' needs norms of the form gain * x * rsqrt(mean(x^2) + eps)")
+        self.hidden = int(self.param("hidden_size"))
+        self._ff_leaves_bias = feed_forward is not None and hasattr(feed_forward, "output_bias")
+
+    def _join(self, stream, pending, ctx, norm=None):
+        """Adds ``pending`` to the stream; with ``norm`` also returns that norm of the sum."""
+        t = ctx.n_tokens
+        y = None if norm is None else ctx.workspace.get("normed", (t, self.hidden), self.dtype)
+        if isinstance(pending, PostNormed):
+            gain_post, eps_post = pending.norm.deferrable()
+            gain, eps = norm.deferrable() if norm is not None else (None, 0.0)
+            kernels.rmsnorm_post_add(y, stream, pending.a, gain_post, eps_post, gain, eps, weight_a=pending.weight_a,
+                                     b=pending.b, weight_b=pending.weight_b, bias=pending.bias, n_rows=t)
+            return y
+        if norm is None:
+            if pending is not None:
+                kernels.add_residual(stream, pending, n_rows=t)
+            return None
+        return norm.forward(stream, ctx, add=pending)
+
+    def collapse(self, stream, pending, ctx):
+        if isinstance(pending, PostNormed):
+            self._join(stream, pending, ctx)
+            pending = None
+        return stream, pending
+
+    def forward(self, stream, pending, ctx, entry, writes_cache=True):
+        a = self._join(stream, pending, ctx, self.norms["pre_mixer"])
+        mixed = PostNormed(self.mixer.forward(a, ctx, entry, writes_cache), self.norms["post_mixer"])
+        if self.feed_forward is None:
+            return mixed
+        h = self._join(stream, mixed, ctx, self.norms["pre_feed_forward"])
+        if self._ff_leaves_bias:
+            f = self.feed_forward.forward(h, ctx, leave_bias=True)
+            return PostNormed(f, self.norms["post_feed_forward"], bias=self.feed_forward.output_bias)
+        return PostNormed(self.feed_forward.forward(h, ctx), self.norms["post_feed_forward"])

@@ -120,3 +120,101 @@ class ChannelDelta(Mixer):
         y = ws.get("attn_out", (t, nh * e), self.dtype)
         kernels.delta_out_norm(y, o, gate, self.norm_w, self.eps, ctx.positions, t, self.shape())
         return linear(y, self.w_o, ctx, "attn_proj", n_rows=t)
+
+
+@register_part("mixer", "head_delta")
+class HeadDelta(Mixer):
+    """Gated delta rule with ONE decay per head (the gated delta network): the recurrence of
+    :class:`ChannelDelta` with a scalar in place of the decay vector, plain projections in place of its
+    low-rank pairs, and a SiLU output gate.
+
+        q, k = silu(conv(W_q h)), silu(conv(W_k h))      unit vectors per head; q also times d^-1/2
+        v    = silu(conv(W_v h));   beta = sigmoid(W_b h)
+        g    = exp(-exp(A_log) * softplus(W_a h + dt_bias))                     one per head
+        S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q             (S is [d, e] per head)
+        y    = W_o [ o / rms(o) * w_norm * silu(W_g h) ]                         (rms per head over e)
+
+    The state of a sequence - S of every head in 32-bit and the convolution's last K - 1 inputs - is one
+    ``state`` cache entry.  Everything between the projections and W_o is computed in 32-bit, with the
+    kernels of the per-channel form.  Parameters: ``hidden_size``, ``num_heads`` (H), ``num_kv_heads``
+    (G), ``head_dim`` (d), ``v_dim`` (e), ``conv`` (K), ``eps``.  Tensors: ``q``, ``k`` [G d, hidden],
+    ``v`` [H e, hidden], ``q_conv``, ``k_conv``, ``v_conv`` [channels, K], ``b``, ``a`` [H, hidden],
+    ``A_log``, ``dt_bias`` [H], ``g`` [H e, hidden], ``norm`` [e], ``o`` [hidden, H e].
+    """
+
+    @classmethod
+    def tensors(cls, spec):
+        p, w = spec.params, spec.weights
+        hid, nh, g, d, e, k = (p["hidden_size"], p["num_heads"], p["num_kv_heads"], p["head_dim"], p["v_dim"],
+                               p["conv"])
+        return [TensorSpec(w["q"], (g * d, hid)), TensorSpec(w["k"], (g * d, hid)), TensorSpec(w["v"], (nh * e, hid)),
+                TensorSpec(w["q_conv"], (g * d, k)), TensorSpec(w["k_conv"], (g * d, k)),
+                TensorSpec(w["v_conv"], (nh * e, k)), TensorSpec(w["b"], (nh, hid)), TensorSpec(w["a"], (nh, hid)),
+                TensorSpec(w["A_log"], (nh,)), TensorSpec(w["dt_bias"], (nh,)), TensorSpec(w["g"], (nh * e, hid)),
+                TensorSpec(w["norm"], (e,), "gain"), TensorSpec(w["o"], (hid, nh * e))]
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        g = lambda n: int(self.param(n))
+        self.hidden, self.num_heads, self.num_kv_heads = g("hidden_size"), g("num_heads"), g("num_kv_heads")
+        self.head_dim, self.v_dim, self.taps = g("head_dim"), g("v_dim"), g("conv")
+        self.eps = float(self.param("eps"))
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("head_delta: num_heads must be a multiple of num_kv_heads")
+        if self.taps < 1:
+            raise ValueError("head_delta: the convolution has at least one tap")
+        self.rows = kernels.delta_state_rows(self.head_dim)
+        self.channels = 2 * self.num_kv_heads * self.head_dim + self.num_heads * self.v_dim
+        self.s_values = self.num_heads * self.v_dim * self.rows
+        self.w_in = self.w_o = self.conv_w = self.dt_bias = self.a_log = self.norm_w = None
+
+    def cache_spec(self):
+        # (a multiple of four values, so that every slot's S starts on a 16-byte boundary)
+        return CacheSpec("state", shape=(-(-(self.s_values + self.channels * (self.taps - 1)) // 4) * 4,))
+
+    def load(self, tensors):
+        w, f32 = self.spec.weights, torch.float32
+        # one product for everything that reads the input: [q | k | v | beta | a | g] (zero rows up to a
+        # multiple of 64, as the per-channel form has them)
+        rows = [tensors[w[n]] for n in ("q", "k", "v", "b", "a", "g")]
+        n = sum(r.shape[0] for r in rows)
+        rows.append(torch.zeros((-n % 64, self.hidden), dtype=rows[0].dtype, device=rows[0].device))
+        self.w_in = torch.cat(rows, 0).to(self.dtype).contiguous()
+        self.conv_w = torch.cat([tensors[w["q_conv"]], tensors[w["k_conv"]], tensors[w["v_conv"]]], 0) \
+            .to(f32).contiguous()
+        self.dt_bias = tensors[w["dt_bias"]].to(f32).contiguous()
+        self.a_log = tensors[w["A_log"]].to(f32).contiguous()
+        self.norm_w = tensors[w["norm"]].to(f32).contiguous()
+        self.w_o = tensors[w["o"]].to(self.dtype).contiguous()
+
+    def shape(self):
+        """The per-channel kernels' shape: the decay logits and the gate stand where its two low-rank
+        first halves do."""
+        return (self.num_heads, self.num_kv_heads, self.head_dim, self.v_dim, self.taps, self.num_heads,
+                self.num_heads * self.v_dim)
+
+    def forward(self, x, ctx, entry, writes_cache=True):
+        t, ws, f32 = ctx.n_tokens, ctx.workspace, torch.float32
+        nh, g, d, e = self.num_heads, self.num_kv_heads, self.head_dim, self.v_dim
+        state = entry.state                                  # [slots, values] 32-bit
+        proj = linear(x, self.w_in, ctx, "delta_in", n_rows=t, out_dtype=f32, wide_f32="library")
+        qn = ws.get("delta_q", (t, g * d), f32)
+        kn = ws.get("delta_k", (t, g * d), f32)
+        vc = ws.get("delta_v", (t, nh * e), f32)
+        beta = ws.get("delta_beta", (t, nh), f32)
+        decay = ws.get("delta_head_decay", (t, nh), f32)
+        unused = ws.get("delta_head_dt", (t, nh), f32)
+        col_a = self.channels + nh
+        kernels.ssm_gates(decay, unused, proj, col_a, self.dt_bias, self.a_log, t, nh)
+        kernels.delta_prepare(qn, kn, vc, beta, proj, t, self.conv_w, state, self.s_values, ctx.positions,
+                              ctx.token_slot, self.shape())
+        if writes_cache:
+            kernels.delta_conv_tail(state, self.s_values, proj, ctx.cu_seqlens, ctx.positions, ctx.token_slot,
+                                    ctx.n_seqs, self.channels, self.taps)
+        o = ws.get("delta_o", (t, nh * e), f32)
+        kernels.delta_scan(o, qn, kn, vc, beta, decay, state, ctx.cu_seqlens, ctx.positions, ctx.token_slot,
+                           ctx.n_seqs, nh, g, d, e, n_tokens=t, decay_per_head=True)
+        y = ws.get("attn_out", (t, nh * e), self.dtype)
+        kernels.delta_out_norm(y, o, proj[:, col_a + nh:], self.norm_w, self.eps, ctx.positions, t, self.shape(),
+                               gate_activation="silu")
+        return linear(y, self.w_o, ctx, "attn_proj", n_rows=t)

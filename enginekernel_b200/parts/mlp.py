@@ -74,3 +74,52 @@ class GatedMLP(FeedForward):
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
             kernels.act_mul(act, gu, self.activation, n_rows=t)
         return linear(act, self.w_down, ctx, "mlp_down", n_rows=t, defer=defer, image=self.product_image)
+
+
+@register_part("feed_forward", "dense_mlp")
+class DenseMLP(FeedForward):
+    """Feed-forward without a gate: down(act(up(x) + b_up)) + b_down; act is the tanh form of GELU or SiLU.
+    Parameters: ``hidden_size``, ``intermediate_size``, ``activation`` ("gelu_tanh", the default, or "silu"),
+    ``bias`` (True: both products have one).  Tensors: ``up`` [I, H], ``down`` [H, I], and with biases
+    ``up_bias`` [I], ``down_bias`` [H].  The first bias and the activation are one pass over the up
+    product's rows; the last bias is added here, or - ``forward(..., leave_bias=True)`` - left to the
+    consumer as ``output_bias`` (a block whose norm kernel reads the result anyway)."""
+
+    @classmethod
+    def tensors(cls, spec):
+        p, w = spec.params, spec.weights
+        h, i = p["hidden_size"], p["intermediate_size"]
+        out = [TensorSpec(w["up"], (i, h)), TensorSpec(w["down"], (h, i))]
+        if p.get("bias"):
+            out += [TensorSpec(w["up_bias"], (i,)), TensorSpec(w["down_bias"], (h,))]
+        return out
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.hidden = int(self.param("hidden_size"))
+        self.inter = int(self.param("intermediate_size"))
+        self.activation = spec.params.get("activation", "gelu_tanh")
+        if self.activation not in ("gelu_tanh", "silu"):
+            raise ValueError(f"dense_mlp has no activation {self.activation!r} (gelu_tanh, silu)")
+        self.biased = bool(spec.params.get("bias"))
+        self.w_up = self.w_down = self.up_bias = self.output_bias = None
+
+    def load(self, tensors):
+        w = self.spec.weights
+        self.w_up = tensors[w["up"]].to(self.dtype).contiguous()
+        self.w_down = tensors[w["down"]].to(self.dtype).contiguous()
+        if self.biased:
+            self.up_bias = tensors[w["up_bias"]].to(torch.float32).contiguous()
+            self.output_bias = tensors[w["down_bias"]].to(torch.float32).contiguous()
+
+    def forward(self, x, ctx, leave_bias=False):
+        t = ctx.n_tokens
+        up = linear(x, self.w_up, ctx, "mlp_up", n_rows=t)
+        act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
+        kernels.bias_act(act, up, self.up_bias, self.activation, n_rows=t)
+        down = linear(act, self.w_down, ctx, "mlp_down", n_rows=t)
+        if self.output_bias is not None and not leave_bias:
+            out = ctx.workspace.get("mlp_down_biased", (t, self.hidden), self.dtype)
+            kernels.bias_act(out, down, self.output_bias, None, n_rows=t)
+            return out
+        return down

@@ -2,7 +2,8 @@
 
 y = gain * x * rsqrt(mean(x^2) + eps), in 32-bit, with the preceding residual add folded
 in when there is one (engine/ek_kernels.py:89-123; gain is a plain factor, no +1, no
-bias).  Parameters: ``size``, ``eps``.  Tensor: ``gain`` [size].
+bias).  Parameters: ``size``, ``eps``, and optionally ``one_plus``: the stored weight w lies
+around zero and the factor is 1 + w (formed once at load, in 32-bit).  Tensor: ``gain`` [size].
 """
 
 from __future__ import annotations
@@ -19,15 +20,19 @@ from .spec import TensorSpec
 class RMSNorm(Norm):
     @classmethod
     def tensors(cls, spec):
-        return [TensorSpec(spec.weights["gain"], (spec.params["size"],), "gain")]
+        return [TensorSpec(spec.weights["gain"], (spec.params["size"],),
+                           "around_zero" if spec.params.get("one_plus") else "gain")]
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
         self.size, self.eps = int(self.param("size")), float(self.param("eps"))
+        self.one_plus = bool(spec.params.get("one_plus"))
         self.gain = None
 
     def load(self, tensors):
         self.gain = tensors[self.spec.weights["gain"]].to(torch.float32).contiguous()
+        if self.one_plus:
+            self.gain = (self.gain + 1.0).contiguous()
 
     def bytes_read_per_step(self, n_tokens):
         return self.gain.numel() * self.gain.element_size()

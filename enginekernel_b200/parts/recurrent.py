@@ -1,4 +1,5 @@
-"""Two recurrent mixers with a decay per head and token, over one scan kernel.
+"""Two recurrent mixers with a decay per head and token, over one scan kernel, and one with a decay per
+channel and no matrix state (``gated_linear_recurrence``, described at its class).
 
 Both keep a matrix S [key size, value size] per head and sequence in 32-bit and update it token by token,
 
@@ -181,4 +182,87 @@ class MatrixMemory(Mixer):
                            n_tokens=t)
         y = ws.get("attn_out", (t, nh * e), self.dtype)
         kernels.xlstm_out(y, o, m_run, proj, col_g, self.norm_w, self.eps, d ** -0.5, ctx.positions, t, nh, e)
+        return linear(y, self.w_o, ctx, "attn_proj", n_rows=t)
+
+
+@register_part("mixer", "gated_linear_recurrence")
+class GatedLinearRecurrence(Mixer):
+    """The recurrent block of Griffin around a real-gated linear recurrent unit.  With R = ``width`` channels
+    in ``blocks`` equal parts and a causal convolution of K taps per channel (bias, no activation):
+
+        y = gelu_tanh(W_y h + b_y)                      u = conv(W_x h + b_x)
+        r = sigmoid(A[p] u_p + a_bias),  i = sigmoid(I[p] u_p + i_bias)        per part p, square matrices
+        a = exp(-rate * r * softplus(lam))              S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t
+        out = W_o (S * y)
+
+    S starts at zero for a new sequence, first token included.  The state of a sequence - S and the
+    convolution's last K - 1 inputs, 32-bit - is one ``state`` cache entry.  The projections' results, the
+    convolution, the gates and S are 32-bit; S * y is rounded once to the activation type.
+
+    Parameters: ``hidden_size``, ``width``, ``blocks``, ``conv``, optional ``rate`` (8, the unit's constant).
+    Tensors: ``y``, ``x`` [R, hidden] with ``y_bias``, ``x_bias`` [R]; ``conv`` [R, K] (last column: the
+    current token), ``conv_bias`` [R]; ``a_gate``, ``i_gate`` [blocks, R / blocks, R / blocks] ([out, in])
+    with ``a_gate_bias``, ``i_gate_bias`` [blocks, R / blocks]; ``lam`` [R]; ``o`` [hidden, R].
+    """
+
+    @classmethod
+    def tensors(cls, spec):
+        p, w = spec.params, spec.weights
+        hid, r, nb, k = p["hidden_size"], p["width"], p["blocks"], p["conv"]
+        size = r // nb
+        return [TensorSpec(w["y"], (r, hid)), TensorSpec(w["y_bias"], (r,)), TensorSpec(w["x"], (r, hid)),
+                TensorSpec(w["x_bias"], (r,)), TensorSpec(w["conv"], (r, k)), TensorSpec(w["conv_bias"], (r,)),
+                TensorSpec(w["a_gate"], (nb, size, size)), TensorSpec(w["a_gate_bias"], (nb, size)),
+                TensorSpec(w["i_gate"], (nb, size, size)), TensorSpec(w["i_gate_bias"], (nb, size)),
+                TensorSpec(w["lam"], (r,)), TensorSpec(w["o"], (hid, r))]
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        g = lambda n: int(self.param(n))
+        self.hidden, self.width, self.blocks, self.taps = g("hidden_size"), g("width"), g("blocks"), g("conv")
+        self.rate = float(spec.params.get("rate", 8.0))
+        if self.width % self.blocks:
+            raise ValueError("gated_linear_recurrence: blocks must divide the width")
+        if self.taps < 1:
+            raise ValueError("gated_linear_recurrence: the convolution has at least one tap")
+        self.size = self.width // self.blocks
+        self.w_in = self.w_o = self.y_bias = self.x_bias = self.conv_w = self.conv_b = None
+        self.w_a = self.w_i = self.b_a = self.b_i = self.lam = None
+
+    def cache_spec(self):
+        return CacheSpec("state", shape=(-(-(self.width * self.taps) // 4) * 4,))
+
+    def load(self, tensors):
+        w, f32 = self.spec.weights, torch.float32
+        # one product for both branches: [y | x]
+        self.w_in = _padded_rows([tensors[w["y"]], tensors[w["x"]]], self.hidden).to(self.dtype).contiguous()
+        self.y_bias = tensors[w["y_bias"]].to(f32).contiguous()
+        self.x_bias = tensors[w["x_bias"]].to(f32).contiguous()
+        self.conv_w = tensors[w["conv"]].to(f32).contiguous()
+        self.conv_b = tensors[w["conv_bias"]].to(f32).contiguous()
+        # [part][in][out]: neighbouring threads of the gate kernel own neighbouring outputs
+        self.w_a = tensors[w["a_gate"]].to(f32).transpose(1, 2).contiguous()
+        self.w_i = tensors[w["i_gate"]].to(f32).transpose(1, 2).contiguous()
+        self.b_a = tensors[w["a_gate_bias"]].to(f32).reshape(-1).contiguous()
+        self.b_i = tensors[w["i_gate_bias"]].to(f32).reshape(-1).contiguous()
+        self.lam = tensors[w["lam"]].to(f32).contiguous()
+        self.w_o = tensors[w["o"]].to(self.dtype).contiguous()
+
+    def forward(self, x, ctx, entry, writes_cache=True):
+        t, ws, f32, r = ctx.n_tokens, ctx.workspace, torch.float32, self.width
+        state = entry.state                                  # [slots, S | conv tail] 32-bit
+        proj = linear(x, self.w_in, ctx, "lru_in", n_rows=t, out_dtype=f32, wide_f32="library")
+        u = ws.get("lru_u", (t, r), f32)
+        kernels.conv_act(u, proj, r, self.conv_w, self.conv_b, state, r, ctx.positions, ctx.token_slot, t, r,
+                         self.taps, in_bias=self.x_bias, activation=None)
+        if writes_cache:
+            kernels.conv_tail(state, r, proj, r, ctx.cu_seqlens, ctx.positions, ctx.token_slot, ctx.n_seqs, r,
+                              self.taps)
+        a = ws.get("lru_a", (t, r), f32)
+        xin = ws.get("lru_x", (t, r), f32)
+        kernels.lru_gates(a, xin, u, self.w_a, self.b_a, self.w_i, self.b_i, self.lam, self.rate, t, self.blocks,
+                          self.size)
+        y = ws.get("attn_out", (t, r), self.dtype)
+        kernels.lru_scan(y, a, xin, proj, 0, self.y_bias, state, ctx.cu_seqlens, ctx.positions, ctx.token_slot,
+                         ctx.n_seqs, r, write_state=writes_cache, n_tokens=t)
         return linear(y, self.w_o, ctx, "attn_proj", n_rows=t)

@@ -69,12 +69,31 @@ class RunSpec:
     the same step stored there.  ``add_embedding``: right before this run the embedding
     output (what the stream held before the first run) is added to the stream once more -
     for models that run a stretch of layers several times and feed the input in again at
-    the start of each further pass.
+    the start of each further pass.  ``mix_input``: right before this run the stream x becomes
+    W [x ; x0] with x0 the embedding output and W the model's :attr:`ModelSpec.input_mix` tensor -
+    the other way of feeding the input in again, a learned one.  ``more_caches``: further cache
+    entries of a mixer that keeps more than one thing (a pair of mixers side by side: pages for
+    one, a fixed-size state for the other), in the order of its ``extra_cache_specs()``.
     """
     layer: int
     cache: Optional[int] = None
     writes_cache: bool = True
     add_embedding: bool = False
+    mix_input: bool = False
+    more_caches: Tuple[int, ...] = ()
+
+
+@dataclasses.dataclass(frozen=True)
+class PairTableSpec:
+    """A second embedding table, indexed by a hash of a token and the one before it in its sequence:
+    row (previous * mul_prev + current * mul_cur) mod buckets is added to the token's embedding, and row
+    ``buckets`` (the table's last) for a sequence's first token.  The previous token of every live
+    sequence is kept in the cache entry ``cache`` (one 32-bit integer per slot)."""
+    table: TensorSpec            # [buckets + 1, hidden]
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    cache: int
 
 
 @dataclasses.dataclass(frozen=True)
@@ -95,9 +114,16 @@ class ModelSpec:
     logit_multiplier: float = 1.0
     #: tensor names a checkpoint may hold although the model does not read them
     ignorable: Tuple[str, ...] = ()
+    #: a hashed table of token pairs added to the embedding (None: the model has none)
+    pair_table: Optional[PairTableSpec] = None
+    #: [hidden, 2 hidden]: what runs with ``mix_input`` multiply [x ; x0] by
+    input_mix: Optional[TensorSpec] = None
 
     def num_cache_entries(self) -> int:
         used = [r.cache for r in self.schedule if r.cache is not None]
+        used += [c for r in self.schedule for c in r.more_caches]
+        if self.pair_table is not None:
+            used.append(self.pair_table.cache)
         return (max(used) + 1) if used else 0
 
     def check(self) -> None:
@@ -107,7 +133,13 @@ class ModelSpec:
                                                                                      self.hidden_size):
             raise ValueError(f"the position table must be [{self.max_positions}, {self.hidden_size}], "
                              f"not {tuple(self.position_table.shape)}")
-        written = set()
+        if self.input_mix is not None and tuple(self.input_mix.shape) != (self.hidden_size, 2 * self.hidden_size):
+            raise ValueError(f"input_mix must be [{self.hidden_size}, {2 * self.hidden_size}], "
+                             f"not {tuple(self.input_mix.shape)}")
+        if self.pair_table is not None and tuple(self.pair_table.table.shape) != (self.pair_table.buckets + 1,
+                                                                                   self.hidden_size):
+            raise ValueError("the pair table must be [buckets + 1, hidden]")
+        written = set() if self.pair_table is None else {self.pair_table.cache}
         for i, run in enumerate(self.schedule):
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"schedule[{i}] names layer {run.layer}, "
@@ -115,6 +147,14 @@ class ModelSpec:
             if run.add_embedding and i == 0:
                 raise ValueError("schedule[0] cannot add the embedding output again: the stream "
                                  "holds nothing else yet")
+            if run.mix_input and self.input_mix is None:
+                raise ValueError(f"schedule[{i}] mixes the input in, but the model names no input_mix tensor")
+            if run.mix_input and run.add_embedding:
+                raise ValueError(f"schedule[{i}] feeds the input in again in two ways at once")
+            for c in run.more_caches:
+                if c < 0 or c in written or c == run.cache:
+                    raise ValueError(f"schedule[{i}] names the further cache entry {c}, which is negative or taken")
+                written.add(c)
             if run.cache is not None:
                 if run.cache < 0:
                     raise ValueError(f"schedule[{i}] names a negative cache entry")

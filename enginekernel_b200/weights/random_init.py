@@ -2,7 +2,7 @@
 
 The reference has no such mode; its tests build a tiny model with an installed
 package (bench/test_equivalence.py:19-31).  Distributions: matrices and
-embeddings N(0, 0.02), norm gains 1 + N(0, 0.1), drawn tensor by tensor in sorted
+embeddings N(0, 0.02), norm gains 1 + N(0, 0.1) (N(0, 0.1) where the model adds the 1 itself), drawn tensor by tensor in sorted
 name order from one generator, in 32-bit and then rounded to the stored dtype, so a
 folder written from (configuration, seed) is the same on every machine when drawn
 on the CPU.  Drawing on a GPU (for full-size benchmarks) gives other values.
@@ -37,6 +37,8 @@ def random_tensors(expected: Mapping[str, TensorSpec], seed: int, dtype=torch.bf
         t = torch.randn(spec.concrete_shape(), generator=gen, device=dev, dtype=torch.float32)
         if spec.init == "gain":
             t.mul_(GAIN_STD).add_(1.0)
+        elif spec.init == "around_zero":         # weights whose use adds the 1 (norms of the 1 + w form)
+            t.mul_(GAIN_STD)
         else:
             t.mul_(LINEAR_STD)
         out[name] = t.to(dtype)
