@@ -267,3 +267,18 @@ def model_forward(config, w, tokens, return_layers=False, final_one_plus=True):
     x = rms_unit(x, eps) * ((1.0 + fw) if final_one_plus else fw)
     logits = x @ w["head"].to(F64).T
     return (logits, after) if return_layers else logits
+
+
+def forward(config, w, tokens):
+    """Logits [T, vocab] of one sequence."""
+    return model_forward(config, w, tokens)
+
+
+def greedy(config, w, tokens, n_new):
+    """``n_new`` tokens by arg-max, the whole sequence run again for each (slow and plain)."""
+    seq, out = list(tokens), []
+    for _ in range(n_new):
+        nxt = int(model_forward(config, w, seq)[-1].argmax())
+        out.append(nxt)
+        seq.append(nxt)
+    return out
