@@ -5,6 +5,7 @@
     python bench.py --design lopazen [--sizes 0.6b,4b,1b-h64] [--layers L] [--batch B] [--skip-kernels]
     python bench.py --design susalorn [--sizes 1b,2b-dense] [--layers L] [--batch B] [--skip-kernels]
     python bench.py --design bolelix [--sizes 1b,2b] [--layers L] [--batch B] [--skip-kernels]
+    python bench.py --design musavik [--sizes 1b,2b] [--layers L] [--batch B] [--skip-kernels]
 
 The shapes and workloads are the ones BASELINE.json names (its configs[2], [3], [4]):
 
@@ -31,6 +32,9 @@ of the same width, layer count and feed-forward work per token.
 ``--design bolelix`` measures the Bolelix decoder (state-space, windowed-attention and matrix-memory layers in
 turn, every one with gated routed experts beside the mixer) next to the Susalorn decoder of the same width, layer
 count and experts.
+``--design musavik`` measures the Musavik decoder (two gated linear recurrences, then attention with mixed heads
+beside a delta rule, every layer with norms on both sides of its sublayers and a dense feed-forward) next to the
+Bolelix decoder of the same width and layer count.
 One line of JSON is printed.  The inputs of a step (gigabytes of weights) are larger than
 the L2.
 
@@ -432,9 +436,48 @@ def bolelix_configs(size: dict, layers: int, context: int):
     return bolelix, susalorn_configs(size["beside"], layers, context)[0]
 
 
+# Musavik at sizes that resemble real layers, beside the Bolelix decoder - the closest design here: it too has
+# attention behind a window that keeps the first tokens, with a gate on its result, in turn with recurrences behind a
+# short convolution - at the same width, layer count and head sizes.  Layers in turn: recurrence, recurrence, the
+# pair of attention and delta rule; the whole stack is one pass of a loop, so that the input mix runs once a step.
+MUSAVIK_SIZES = {
+    "1b": dict(width=2048, vocab=128256, rglru=dict(width=2048, blocks=8, conv=4),
+               left=dict(heads=16, kv_heads=4, dim=128, vdim=128, rot=64, window=1024, keep_first=4),
+               right=dict(heads=16, kv_heads=8, dim=128, vdim=128, conv=4), ff=6144, pairs=(99991, 127, 17),
+               beside="1b"),
+    "2b": dict(width=2560, vocab=151936, rglru=dict(width=2560, blocks=10, conv=4),
+               left=dict(heads=20, kv_heads=5, dim=128, vdim=128, rot=128, window=512, keep_first=64),
+               right=dict(heads=20, kv_heads=10, dim=128, vdim=128, conv=4), ff=7680, pairs=(199999, 8191, 31),
+               beside="2b"),
+}
+
+
+def musavik_configs(size: dict, layers: int, context: int):
+    """(Musavik configuration, Bolelix configuration) of one size."""
+    from enginekernel_b200.config.musavik import MusavikConfig
+    at = size["left"]
+    left = {"dim": at["dim"], "vdim": at["vdim"], "heads": at["heads"], "kv_heads": at["kv_heads"],
+            "scale": at["dim"] ** -0.5 * 8.0, "rot": {"base": 1000000.0, "dims": at["rot"]},
+            "mask": {"size": at["window"], "keep_first": at["keep_first"]}}
+    mlp = {"kind": "dense", "ff": size["ff"]}
+    made = []
+    for i in range(layers):
+        if i % 3 == 2:
+            made.append({"type": "parallel", "mlp": mlp,
+                         "mixer": {"left": left, "right": dict(size["right"]), "left_scale": 0.8, "right_scale": 0.5}})
+        else:
+            made.append({"type": "rglru", "mixer": dict(size["rglru"]), "mlp": mlp})
+    b, mp, mc = size["pairs"]
+    musavik = MusavikConfig.from_dict({
+        "architecture": "Musavik", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-6},
+        "embedding": {"scale": 1.0, "bigram": {"buckets": b, "mul_prev": mp, "mul_cur": mc}}, "layers": made,
+        "loop": {"start": 0, "stop": layers, "times": 1}})
+    return musavik, bolelix_configs(BOLELIX_SIZES[size["beside"]], layers, context)[0]
+
+
 #: design -> (sizes, configurations of one size, the design it is measured beside)
 DESIGNS = {"lopazen": (DESIGN_SIZES, design_configs, "qwen3"), "susalorn": (SUSALORN_SIZES, susalorn_configs, "qwen3"),
-           "bolelix": (BOLELIX_SIZES, bolelix_configs, "susalorn")}
+           "bolelix": (BOLELIX_SIZES, bolelix_configs, "susalorn"), "musavik": (MUSAVIK_SIZES, musavik_configs, "bolelix")}
 
 
 def measure_design(cfg, vocab, batch, prompt_len, context, steps, warmup, pk, with_kernels):
@@ -560,9 +603,10 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-kernels", action="store_true", help="leave out the per-kernel tables")
     ap.add_argument("--prefill-seqs", type=int, default=1,
                     help="sequences of 2,048 tokens in the prompt step of the per-kernel table")
-    ap.add_argument("--design", default="", choices=["", "lopazen", "susalorn", "bolelix"],
+    ap.add_argument("--design", default="", choices=["", "lopazen", "susalorn", "bolelix", "musavik"],
                     help="instead of the default workload: this design beside the Qwen3 decoder (bolelix: beside "
-                         "the Susalorn decoder) at equal layer sizes (prompt step, decode step, per-kernel tables)")
+                         "the Susalorn decoder; musavik: beside the Bolelix decoder) at equal layer sizes (prompt "
+                         "step, decode step, per-kernel tables)")
     ap.add_argument("--sizes", default="", help="with --design: comma-separated names of DESIGN_SIZES")
     args = ap.parse_args(argv)
 

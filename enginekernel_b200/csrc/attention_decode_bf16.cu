@@ -64,7 +64,8 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
                              int window, int n_splits, int keys_per_split,
                              float* __restrict__ part_acc, float* __restrict__ part_ml,
                              float sink_log2, const float* __restrict__ sinks, int keep_first,
-                             const bf16* __restrict__ gate, int gate_stride) {
+                             const bf16* __restrict__ gate, int gate_stride, int cross,
+                             float* __restrict__ out32) {
   constexpr int D = DCH * 32;
   extern __shared__ float smem[];              // [warps][16][D] accumulators, then [warps][16][2]
   float* o_s = smem;
@@ -73,7 +74,11 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
   pdl_wait();
 
   const int t = blockIdx.x;
-  const int kv_head = blockIdx.y / row_blocks, rb = blockIdx.y % row_blocks;
+  // cross > 1: grid.y also runs over the value heads - the group's weights, taken against its own key
+  // head, are applied to the values of head `v_head`, and the result goes to out32 [T, heads, value heads, D]
+  const int unit = blockIdx.y / cross;
+  const int kv_head = unit / row_blocks, rb = unit % row_blocks;
+  const int v_head = cross > 1 ? (int)(blockIdx.y % cross) : kv_head;
   const int split = blockIdx.z;
   const int group = n_q_heads / cache.heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
@@ -138,7 +143,7 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
       const size_t row0 = ((size_t)page * cache.heads + kv_head) * EK_PAGE + (key0 & (EK_PAGE - 1));
       // this lane's rows: keys key0 + g and key0 + 8 + g, dims 32c + 8 tq .. + 7
       const bf16* kp = kbase + (row0 + g) * D + 8 * tq;
-      const bf16* vp = vbase + (row0 + g) * D + 8 * tq;
+      const bf16* vp = vbase + (((size_t)page * cache.heads + v_head) * EK_PAGE + (key0 & (EK_PAGE - 1)) + g) * D + 8 * tq;
       uint4 kr[2][DCH], vr[2][DCH];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
@@ -252,9 +257,10 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
       if (sk > -INFINITY && l > 0.f) l += exp2f(sk - m);
       float res = l > 0.f ? o / l : 0.f;
       if (gate != nullptr) res *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + head])));
-      out[((size_t)t * n_q_heads + head) * D + d] = __float2bfloat16_rn(res);
+      if (out32) out32[(((size_t)t * n_q_heads + head) * cross + v_head) * D + d] = res;
+      else out[((size_t)t * n_q_heads + head) * D + d] = __float2bfloat16_rn(res);
     } else {
-      const size_t pi = ((size_t)t * n_q_heads + head) * n_splits + split;
+      const size_t pi = (((size_t)t * n_q_heads + head) * cross + (cross > 1 ? v_head : 0)) * n_splits + split;
       part_acc[pi * D + d] = o;
       if (d == 0) {
         part_ml[2 * pi] = m;                   // in units of log2 (scores were scaled by log2 e)
@@ -270,11 +276,14 @@ __global__ void attention_decode_combine_kernel(bf16* __restrict__ out,
                                                 const float* part_ml, int n_q_heads,
                                                 int head_dim, int n_splits, float sink_log2,
                                                 const float* __restrict__ sinks,
-                                                const bf16* __restrict__ gate, int gate_stride) {
-  if (sinks != nullptr) sink_log2 = sinks[blockIdx.y] * 1.4426950408889634f;
+                                                const bf16* __restrict__ gate, int gate_stride, int cross,
+                                                float* __restrict__ out32) {
+  // grid (tokens, heads * cross): with cross > 1 a (head, value head) pair a block, results to out32
+  const int head = blockIdx.y / cross;
+  if (sinks != nullptr) sink_log2 = sinks[head] * 1.4426950408889634f;
   pdl_launch_dependents();
   pdl_wait();
-  const size_t th = (size_t)blockIdx.x * n_q_heads + blockIdx.y;
+  const size_t th = (size_t)blockIdx.x * gridDim.y + blockIdx.y;
   const float* ml = part_ml + 2 * th * n_splits;
   float m = -INFINITY;
   for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
@@ -284,13 +293,14 @@ __global__ void attention_decode_combine_kernel(bf16* __restrict__ out,
   if (sink_log2 > -INFINITY && l > 0.f) l += exp2f(sink_log2 - m);      // the sink, counted once
   float inv = l > 0.f ? 1.f / l : 0.f;
   if (gate != nullptr)
-    inv *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)blockIdx.x * gate_stride + blockIdx.y])));
+    inv *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)blockIdx.x * gate_stride + head])));
   for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < n_splits; ++s)
       if (ml[2 * s + 1] > 0.f)
         acc += part_acc[(th * n_splits + s) * head_dim + i] * exp2f(ml[2 * s] - m);
-    out[th * head_dim + i] = __float2bfloat16_rn(acc * inv);
+    if (out32) out32[th * head_dim + i] = acc * inv;
+    else out[th * head_dim + i] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -299,7 +309,7 @@ static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* pos
                       const int* token_slot, PagedKV cache, int n_tokens, int n_q_heads,
                       float scale, int window, int n_splits, int keys_per_split, float* part_acc,
                       float* part_ml, float sink, const float* sinks, int keep_first, const bf16* gate,
-                      int gate_stride, cudaStream_t stream) {
+                      int gate_stride, cudaStream_t stream, int cross = 1, float* out32 = nullptr) {
   constexpr int D = DCH * 32;
   const int group = n_q_heads / cache.heads;
   const int row_blocks = (group + 15) / 16;
@@ -309,7 +319,8 @@ static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* pos
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(n_tokens, cache.heads * row_blocks, n_splits);
+  dim3 grid(n_tokens, cache.heads * row_blocks * cross, n_splits);
+  if (grid.y > 65535) return EK_ERR_ARG;
   // three blocks an SM (two for the largest head sizes) need this much shared memory; the rest
   // stays L1, which the K/V stream needs for its loads in flight
   const int blocks_per_sm = DCH <= 4 ? 3 : 2;
@@ -319,12 +330,12 @@ static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* pos
                              stream, out, q, q_row_stride, positions, token_slot, cache, n_q_heads,
                              row_blocks, scale * 1.4426950408889634f, window, n_splits,
                              keys_per_split, part_acc, part_ml, sink * 1.4426950408889634f, sinks,
-                             window > 0 ? keep_first : 0, gate, gate_stride);
+                             window > 0 ? keep_first : 0, gate, gate_stride, cross, out32);
   if (e != cudaSuccess || n_splits == 1) return (int)e;
-  dim3 cgrid(n_tokens, n_q_heads);
+  dim3 cgrid(n_tokens, n_q_heads * cross);
   return (int)launch_pdl(attention_decode_combine_kernel, cgrid, dim3(64), 0, stream, out,
                          (const float*)part_acc, (const float*)part_ml, n_q_heads, D, n_splits,
-                         sink * 1.4426950408889634f, sinks, gate, gate_stride);
+                         sink * 1.4426950408889634f, sinks, gate, gate_stride, cross, out32);
 }
 
 }  // namespace ek
@@ -353,6 +364,36 @@ EK_EXPORT int ek_attention_decode_bf16(void* out, const void* q, int q_row_strid
     return launch_dch<DCH>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot, cache, \
                            n_tokens, n_q_heads, scale, window, n_splits, keys_per_split, part_acc, \
                            part_ml, sink, sinks, keep_first, (const bf16*)gate, gate_stride, stream);
+  switch (head_dim / 32) {
+    EK_CASE(1) EK_CASE(2) EK_CASE(3) EK_CASE(4) EK_CASE(5) EK_CASE(6) EK_CASE(7) EK_CASE(8)
+  }
+#undef EK_CASE
+  return EK_ERR_ARG;
+}
+
+// Every query head's weights (against its own key head) applied to the values of every key/value head:
+// out32 [T, heads, kv heads, D] in 32-bit, for designs that mix the heads' weights behind the softmax.
+// The split buffers hold heads * kv heads rows a token.
+EK_EXPORT int ek_attention_decode_cross_bf16(float* out32, const void* q, int q_row_stride,
+                                             const int* positions, const int* token_slot,
+                                             const void* k_pages, const void* v_pages,
+                                             const int* block_table, int table_stride, int n_tokens,
+                                             int n_q_heads, int n_kv_heads, int head_dim, float scale,
+                                             int window, int n_splits, int keys_per_split,
+                                             float* part_acc, float* part_ml, int keep_first,
+                                             cudaStream_t stream) {
+  using namespace ek;
+  if (n_tokens <= 0) return 0;
+  if (head_dim % 32 || head_dim < 32 || head_dim > 256 || n_kv_heads <= 0 || !out32 ||
+      n_q_heads % n_kv_heads || n_splits < 1 || n_splits > 65535 || q_row_stride % 8 ||
+      (n_splits > 1 && (!part_acc || !part_ml || keys_per_split < 0 || keys_per_split % kUnit)))
+    return EK_ERR_ARG;
+  PagedKV cache{(void*)k_pages, (void*)v_pages, block_table, table_stride, n_kv_heads, head_dim};
+#define EK_CASE(DCH)                                                                              \
+  case DCH:                                                                                       \
+    return launch_dch<DCH>(nullptr, (const bf16*)q, q_row_stride, positions, token_slot, cache,   \
+                           n_tokens, n_q_heads, scale, window, n_splits, keys_per_split, part_acc, \
+                           part_ml, -INFINITY, nullptr, keep_first, nullptr, 0, stream, n_kv_heads, out32);
   switch (head_dim / 32) {
     EK_CASE(1) EK_CASE(2) EK_CASE(3) EK_CASE(4) EK_CASE(5) EK_CASE(6) EK_CASE(7) EK_CASE(8)
   }

@@ -9,6 +9,9 @@
 // `keep_first` > 0 (with a window): the first keep_first positions of the sequence stay visible to
 // every later token at their true positions, beside the window.  `gate`, if given, holds one value
 // per token and query head (row stride `gate_stride`): the head's output is multiplied by its sigmoid.
+// `cross` > 1 (entry point ..._cross): every head's weights are applied to the values of every key/value
+// head and the results are kept in 32-bit, for designs that mix the heads' weights behind the softmax;
+// mix_heads_kernel forms the mixed results from them.
 // It serves whole prompts, chunks and single decoded tokens alike, since each token
 // carries its own position and slot; the faster bfloat16 kernels in attention_bf16.cu
 // cover the common head sizes, this one covers everything and is the 32-bit path.
@@ -240,23 +243,33 @@ template <typename T>
 __global__ void mix_heads_kernel(T* __restrict__ out, const float* __restrict__ parts, const float* __restrict__ mix,
                                  const T* __restrict__ gate, int gate_stride, int n_q_heads, int n_kv_heads,
                                  int head_dim, int vdim, const int* __restrict__ positions) {
-  extern __shared__ float mix_s[];              // [H][H]
+  // grid (tokens, value heads): a block stages A[., c] of its token - every head's weights on value head c -
+  // once, and forms the results of the heads that own value head c from it
+  extern __shared__ __align__(16) float mix_s[];              // [H][H] mix, then [H][vdim] parts
+  float* a_s = mix_s + n_q_heads * n_q_heads;
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
-  for (int i = threadIdx.x; i < n_q_heads * n_q_heads; i += blockDim.x) mix_s[i] = mix[i];
-  __syncthreads();
-  const bool live = positions[t] >= 0;
+  const int t = blockIdx.x, c = blockIdx.y;
   const int per = n_q_heads / n_kv_heads;
-  const float* a = parts + (size_t)t * n_q_heads * n_kv_heads * head_dim;
+  if (positions[t] < 0) {                       // a row of a finished sequence: zeros
+    for (int i = threadIdx.x; i < per * vdim; i += blockDim.x)
+      out[(size_t)t * n_q_heads * vdim + (size_t)c * per * vdim + i] = from_f<T>(0.f);
+    return;
+  }
+  for (int i = threadIdx.x; i < n_q_heads * n_q_heads; i += blockDim.x) mix_s[i] = mix[i];
+  const float* a = parts + ((size_t)t * n_q_heads * n_kv_heads + c) * head_dim;
   for (int i = threadIdx.x; i < n_q_heads * vdim; i += blockDim.x) {
-    const int h = i / vdim, j = i % vdim, c = h / per;
+    const int g = i / vdim, j = i % vdim;
+    a_s[i] = a[(size_t)g * n_kv_heads * head_dim + j];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < per * vdim; i += blockDim.x) {
+    const int h = c * per + i / vdim, j = i % vdim;
     float acc = 0.f;
-    if (live)
-      for (int g = 0; g < n_q_heads; ++g)
-        acc = fmaf(mix_s[h * n_q_heads + g], a[((size_t)g * n_kv_heads + c) * head_dim + j], acc);
-    if (gate != nullptr && live) acc *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)t * gate_stride + i])));
-    out[(size_t)t * n_q_heads * vdim + i] = from_f<T>(acc);
+    for (int g = 0; g < n_q_heads; ++g) acc = fmaf(mix_s[h * n_q_heads + g], a_s[g * vdim + j], acc);
+    const size_t at = (size_t)h * vdim + j;
+    if (gate != nullptr) acc *= 1.f / (1.f + expf(-to_f<T>(gate[(size_t)t * gate_stride + at])));
+    out[(size_t)t * n_q_heads * vdim + at] = from_f<T>(acc);
   }
 }
 
@@ -298,9 +311,16 @@ __global__ void mix_heads_kernel(T* __restrict__ out, const float* __restrict__ 
     if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || vdim <= 0 || vdim > head_dim || \
         n_q_heads > 96 || (gate && gate_stride < n_q_heads * vdim))                            \
       return EK_ERR_ARG;                                                                       \
-    return (int)ek::launch_pdl(ek::mix_heads_kernel<T>, dim3(n_tokens), dim3(256),             \
-                               (size_t)n_q_heads * n_q_heads * sizeof(float), stream, (T*)out, parts, mix, \
-                               (const T*)gate, gate_stride, n_q_heads, n_kv_heads, head_dim, vdim, positions); \
+    const size_t smem = (size_t)n_q_heads * (n_q_heads + vdim) * sizeof(float);                \
+    if (smem > 200 * 1024 || n_kv_heads > 65535) return EK_ERR_ARG;                            \
+    if (smem > 40 * 1024) {                                                                    \
+      cudaError_t e = cudaFuncSetAttribute(ek::mix_heads_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)smem);                                         \
+      if (e != cudaSuccess) return (int)e;                                                     \
+    }                                                                                          \
+    return (int)ek::launch_pdl(ek::mix_heads_kernel<T>, dim3(n_tokens, n_kv_heads), dim3(128), smem, stream, \
+                               (T*)out, parts, mix, (const T*)gate, gate_stride, n_q_heads, n_kv_heads, \
+                               head_dim, vdim, positions);                                     \
   }
 
 EK_INSTANTIATE(f32, float)

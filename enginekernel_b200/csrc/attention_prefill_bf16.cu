@@ -64,7 +64,8 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
                               const int* __restrict__ cu_seqlens, int n_seqs, PagedKV cache,
                               int n_q_heads, float scale_log2, int window, int tok_per_tile,
                               float sink_log2, const float* __restrict__ sinks, int keep_first,
-                              const bf16* __restrict__ gate, int gate_stride) {
+                              const bf16* __restrict__ gate, int gate_stride, int cross,
+                              float* __restrict__ out32) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int tile_info[3];                 // first token (packed index), tokens, sequence
   const int D = cache.head_dim;
@@ -74,7 +75,11 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   bf16* v_s = k_s + 2 * kPfKeys * LD;                       // [2][64][LD]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
-  const int kv_head = blockIdx.x;             // heads fastest: longest key ranges start first
+  // heads fastest: longest key ranges start first.  cross > 1: grid.x runs over (key head, value head)
+  // pairs - the group's weights, taken against its own key head, are applied to another head's values,
+  // and the result goes to out32 [T, heads, value heads, D] in 32-bit
+  const int kv_head = blockIdx.x / cross;
+  const int v_head = cross > 1 ? (int)(blockIdx.x % cross) : kv_head;
   const int group = n_q_heads / cache.heads;
 
   if (tid == 0) {
@@ -101,8 +106,9 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
   if (pos0 < 0) {                              // rows of a finished sequence: zeros
     for (int i = tid; i < n_rows * D; i += blockDim.x) {
       const int r = i / D, d = i % D;
-      out[((size_t)(t_first + r / group) * n_q_heads + kv_head * group + r % group) * D + d] =
-          __float2bfloat16_rn(0.f);
+      const size_t head_at = (size_t)(t_first + r / group) * n_q_heads + kv_head * group + r % group;
+      if (out32) out32[(head_at * cross + v_head) * D + d] = 0.f;
+      else out[head_at * D + d] = __float2bfloat16_rn(0.f);
     }
     return;
   }
@@ -132,7 +138,7 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     const int page = table[kt];
     const size_t base = ((size_t)page * cache.heads + kv_head) * EK_PAGE * (size_t)D;
     const bf16* ksrc = (const bf16*)cache.k + base;
-    const bf16* vsrc = (const bf16*)cache.v + base;
+    const bf16* vsrc = (const bf16*)cache.v + ((size_t)page * cache.heads + v_head) * EK_PAGE * (size_t)D;
     bf16* kd = k_s + buf * kPfKeys * LD;
     bf16* vd = v_s + buf * kPfKeys * LD;
     for (int i = tid; i < kPfKeys * chunks; i += blockDim.x) {
@@ -294,14 +300,20 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     const int d = 8 * i + 2 * tq;
     if (d < D) {
       if (row_lo < n_rows) {
-        bf16* o = out + ((size_t)(t_first + row_lo / group) * n_q_heads + kv_head * group +
-                         row_lo % group) * D + d;
-        *reinterpret_cast<uint32_t*>(o) = pack2(o_acc[i][0] * inv_lo, o_acc[i][1] * inv_lo);
+        const size_t at = (size_t)(t_first + row_lo / group) * n_q_heads + kv_head * group + row_lo % group;
+        if (out32)
+          *reinterpret_cast<float2*>(out32 + (at * cross + v_head) * D + d) =
+              make_float2(o_acc[i][0] * inv_lo, o_acc[i][1] * inv_lo);
+        else
+          *reinterpret_cast<uint32_t*>(out + at * D + d) = pack2(o_acc[i][0] * inv_lo, o_acc[i][1] * inv_lo);
       }
       if (row_hi < n_rows) {
-        bf16* o = out + ((size_t)(t_first + row_hi / group) * n_q_heads + kv_head * group +
-                         row_hi % group) * D + d;
-        *reinterpret_cast<uint32_t*>(o) = pack2(o_acc[i][2] * inv_hi, o_acc[i][3] * inv_hi);
+        const size_t at = (size_t)(t_first + row_hi / group) * n_q_heads + kv_head * group + row_hi % group;
+        if (out32)
+          *reinterpret_cast<float2*>(out32 + (at * cross + v_head) * D + d) =
+              make_float2(o_acc[i][2] * inv_hi, o_acc[i][3] * inv_hi);
+        else
+          *reinterpret_cast<uint32_t*>(out + at * D + d) = pack2(o_acc[i][2] * inv_hi, o_acc[i][3] * inv_hi);
       }
     }
   }
@@ -312,7 +324,7 @@ static int launch_dmax(bf16* out, const bf16* q, int q_row_stride, const int* po
                        const int* token_slot, const int* cu_seqlens, int n_seqs, int n_tokens,
                        PagedKV cache, int n_q_heads, float scale, int window, float sink,
                        const float* sinks, int keep_first, const bf16* gate, int gate_stride,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, int cross = 1, float* out32 = nullptr) {
   const int group = n_q_heads / cache.heads;
   const int tok_per_tile = kPfRows / group;
   const int D = cache.head_dim, LD = D + 8;
@@ -322,16 +334,41 @@ static int launch_dmax(bf16* out, const bf16* q, int q_row_stride, const int* po
   if (e != cudaSuccess) return (int)e;
   prefer_carveout((const void*)attention_prefill_bf16_kernel<DMAX>, 100);
   const int tiles = (n_tokens + tok_per_tile - 1) / tok_per_tile + n_seqs;   // upper bound
-  dim3 grid(cache.heads, tiles);
+  dim3 grid(cache.heads * cross, tiles);
   if (tiles > 65535) return EK_ERR_ARG;
   attention_prefill_bf16_kernel<DMAX><<<grid, kPfWarps * 32, smem, stream>>>(
       out, q, q_row_stride, positions, token_slot, cu_seqlens, n_seqs, cache, n_q_heads,
       scale * 1.4426950408889634f, window, tok_per_tile, sink * 1.4426950408889634f, sinks,
-      window > 0 ? keep_first : 0, gate, gate_stride);
+      window > 0 ? keep_first : 0, gate, gate_stride, cross, out32);
   EK_RETURN_LAUNCH_STATUS();
 }
 
 }  // namespace ek
+
+// Every query head's weights (against its own key head) applied to the values of every key/value head:
+// out32 [T, heads, kv heads, D] in 32-bit, for designs that mix the heads' weights behind the softmax.
+EK_EXPORT int ek_attention_prefill_cross_bf16(float* out32, const void* q, int q_row_stride,
+                                              const int* positions, const int* token_slot,
+                                              const int* cu_seqlens, int n_seqs, int n_tokens,
+                                              const void* k_pages, const void* v_pages,
+                                              const int* block_table, int table_stride, int n_q_heads,
+                                              int n_kv_heads, int head_dim, float scale, int window,
+                                              int keep_first, cudaStream_t stream) {
+  using namespace ek;
+  if (n_tokens <= 0 || n_seqs <= 0) return 0;
+  if (head_dim % 16 || head_dim < 16 || head_dim > 256 || n_kv_heads <= 0 || !out32 ||
+      n_q_heads % n_kv_heads || n_q_heads / n_kv_heads > kPfRows || q_row_stride % 8)
+    return EK_ERR_ARG;
+  PagedKV cache{(void*)k_pages, (void*)v_pages, block_table, table_stride, n_kv_heads, head_dim};
+#define EK_CROSS(DMAX)                                                                                   \
+  return launch_dmax<DMAX>(nullptr, (const bf16*)q, q_row_stride, positions, token_slot, cu_seqlens,     \
+                           n_seqs, n_tokens, cache, n_q_heads, scale, window, -INFINITY, nullptr,        \
+                           keep_first, nullptr, 0, stream, n_kv_heads, out32)
+  if (head_dim <= 64) EK_CROSS(64);
+  if (head_dim <= 128) EK_CROSS(128);
+  EK_CROSS(256);
+#undef EK_CROSS
+}
 
 // head_dim a multiple of 16 up to 256; the group (query heads per KV head) at most 128.
 // Tokens of a sequence must stand at consecutive positions in the step.

@@ -347,6 +347,37 @@ __global__ void rmsnorm_post_add_kernel(T* __restrict__ y, float* resid, const T
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = from_f<T>(x_s[i] * rstd * gain[i]);
 }
 
+// Four neighbouring values a thread, a row a block row (grid (rows, column tiles)): for widths, offsets and
+// strides that are multiples of 4 and pointers on 16-byte boundaries.
+template <typename T>
+__global__ void cast_columns4_kernel(T* __restrict__ dst, int dst_stride, int col0, const float* __restrict__ src,
+                                     int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= width) return;
+  const size_t r = blockIdx.x;
+  Vec4<T>::store(dst + r * dst_stride + col0 + c, *reinterpret_cast<const float4*>(src + r * width + c));
+}
+
+template <typename T, typename X>
+__global__ void bias_act4_kernel(T* __restrict__ out, const X* __restrict__ x, int x_stride, int col0,
+                                 const float* __restrict__ bias, int width, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= width) return;
+  const size_t r = blockIdx.x;
+  float4 v = Vec4<X>::load(x + r * x_stride + col0 + c);
+  if (bias) {
+    const float4 b = *reinterpret_cast<const float4*>(bias + c);
+    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+  }
+  if (act == 1) v = make_float4(silu_of<T, 1>(v.x), silu_of<T, 1>(v.y), silu_of<T, 1>(v.z), silu_of<T, 1>(v.w));
+  else if (act == 2) v = make_float4(silu_of<T, 0>(v.x), silu_of<T, 0>(v.y), silu_of<T, 0>(v.z), silu_of<T, 0>(v.w));
+  Vec4<T>::store(out + r * width + c, v);
+}
+
 // out[r, i] = act(x[r, col0 + i] + bias[i]) for i < width; act 0: none, 1: the tanh form of GELU, 2: SiLU.
 // x is 32-bit or T (`x_is_f32`), rows `x_stride` apart.
 template <typename T>
@@ -510,6 +541,10 @@ using namespace ek;
     if (n_rows <= 0) return 0;                                                                  \
     if (width <= 0 || col0 < 0 || dst_stride < col0 + width) return EK_ERR_ARG;                 \
     const size_t n = (size_t)n_rows * width;                                                    \
+    if (width % 4 == 0 && col0 % 4 == 0 && dst_stride % 4 == 0 && (((uintptr_t)dst | (uintptr_t)src) & 15) == 0 \
+        && (width + 1023) / 1024 <= 65535)                                                      \
+      return (int)ek::launch_pdl(ek::cast_columns4_kernel<T>, dim3(n_rows, (width + 1023) / 1024), dim3(256), 0, \
+                                 stream, (T*)dst, dst_stride, col0, src, width);                \
     return (int)ek::launch_pdl(ek::cast_columns_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, \
                                stream, (T*)dst, dst_stride, col0, src, width, n);               \
   }                                                                                             \
@@ -536,6 +571,15 @@ using namespace ek;
     if (n_rows <= 0) return 0;                                                                  \
     if (width <= 0 || col0 < 0 || x_stride < col0 + width || act < 0 || act > 2) return EK_ERR_ARG; \
     const size_t n = (size_t)n_rows * width;                                                    \
+    if (width % 4 == 0 && col0 % 4 == 0 && x_stride % 4 == 0 && (width + 1023) / 1024 <= 65535 && \
+        (((uintptr_t)out | (uintptr_t)x | (uintptr_t)bias) & 15) == 0) {                        \
+      const dim3 grid(n_rows, (width + 1023) / 1024);                                           \
+      if (x_is_f32)                                                                             \
+        return (int)ek::launch_pdl(ek::bias_act4_kernel<T, float>, grid, dim3(256), 0, stream, (T*)out, \
+                                   (const float*)x, x_stride, col0, bias, width, act);          \
+      return (int)ek::launch_pdl(ek::bias_act4_kernel<T, T>, grid, dim3(256), 0, stream, (T*)out, (const T*)x, \
+                                 x_stride, col0, bias, width, act);                             \
+    }                                                                                           \
     return (int)ek::launch_pdl(ek::bias_act_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, \
                                stream, (T*)out, x, x_is_f32, x_stride, col0, bias, width, n, act); \
   }                                                                                             \

@@ -107,24 +107,24 @@ __global__ void conv_tail_kernel(float* __restrict__ state, size_t slot_stride, 
 //     r = sigmoid(W_a[p] u_p + b_a),  i = sigmoid(W_i[p] u_p + b_i)          (square matrices per part)
 //     log a = -rate * r * softplus(lam),  a = exp(log a),  x = sqrt(1 - a^2) * i * u
 // so that the recurrence itself is S_t = a_t S_(t-1) + x_t.  1 - a^2 is taken as -expm1(2 log a), which
-// keeps its digits when a is close to 1.  grid (token tiles of 16, parts, output tiles of 128); a block
-// stages its tokens' u_p in shared memory, a thread owns one output channel for all 16 tokens, and the
+// keeps its digits when a is close to 1.  grid (token tiles of 32, parts, output tiles of 128); a block
+// stages its tokens' u_p in shared memory, a thread owns one output channel for all 32 tokens, and the
 // weights come transposed ([in][out]) so that neighbouring threads read neighbouring words.
-constexpr int kLruTokens = 16;
+constexpr int kLruTokens = 32;
 __global__ void __launch_bounds__(128)
 lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ x_out, const float* __restrict__ u, int u_stride,
                  const float* __restrict__ w_a, const float* __restrict__ b_a, const float* __restrict__ w_i,
                  const float* __restrict__ b_i, const float* __restrict__ lam, float rate, int n_tokens, int parts,
                  int size) {
-  extern __shared__ __align__(16) float u_s[];     // [kLruTokens][size]
+  extern __shared__ __align__(16) float u_s[];     // [kLruTokens][ld], ld = size rounded up to 4
   pdl_launch_dependents();
   pdl_wait();
   const int t0 = blockIdx.x * kLruTokens, p = blockIdx.y, tid = threadIdx.x;
   const int nt = min(kLruTokens, n_tokens - t0);
-  const int R = parts * size;
-  for (int idx = tid; idx < kLruTokens * size; idx += blockDim.x) {
-    const int tt = idx / size, r = idx % size;
-    u_s[idx] = tt < nt ? u[(size_t)(t0 + tt) * u_stride + p * size + r] : 0.f;
+  const int R = parts * size, ld = (size + 3) & ~3;
+  for (int idx = tid; idx < kLruTokens * ld; idx += blockDim.x) {
+    const int tt = idx / ld, r = idx % ld;
+    u_s[idx] = (tt < nt && r < size) ? u[(size_t)(t0 + tt) * u_stride + p * size + r] : 0.f;
   }
   __syncthreads();
   const int o = blockIdx.z * 128 + tid;
@@ -136,11 +136,23 @@ lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ x_out, const flo
   for (int tt = 0; tt < kLruTokens; ++tt) { ra[tt] = ba; ri[tt] = bi; }
   const float* wa = w_a + (size_t)p * size * size + o;
   const float* wi = w_i + (size_t)p * size * size + o;
-  for (int r = 0; r < size; ++r) {
+  int r = 0;
+  for (; r + 4 <= size; r += 4) {               // eight weights, then one 16-byte read of a token's four inputs
+    float va[4], vi[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { va[j] = wa[(size_t)(r + j) * size]; vi[j] = wi[(size_t)(r + j) * size]; }
+#pragma unroll
+    for (int tt = 0; tt < kLruTokens; ++tt) {
+      const float4 x = *reinterpret_cast<const float4*>(u_s + tt * ld + r);
+      ra[tt] = fmaf(va[3], x.w, fmaf(va[2], x.z, fmaf(va[1], x.y, fmaf(va[0], x.x, ra[tt]))));
+      ri[tt] = fmaf(vi[3], x.w, fmaf(vi[2], x.z, fmaf(vi[1], x.y, fmaf(vi[0], x.x, ri[tt]))));
+    }
+  }
+  for (; r < size; ++r) {
     const float va = wa[(size_t)r * size], vi = wi[(size_t)r * size];
 #pragma unroll
     for (int tt = 0; tt < kLruTokens; ++tt) {
-      const float x = u_s[tt * size + r];
+      const float x = u_s[tt * ld + r];
       ra[tt] = fmaf(va, x, ra[tt]);
       ri[tt] = fmaf(vi, x, ri[tt]);
     }
@@ -152,8 +164,65 @@ lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ x_out, const flo
       const float log_a = -sp * sigmoid_f(ra[tt]);
       const size_t at = (size_t)(t0 + tt) * R + c;
       a_out[at] = expf(log_a);
-      x_out[at] = sqrtf(-expm1f(2.f * log_a)) * sigmoid_f(ri[tt]) * u_s[tt * size + o];
+      x_out[at] = sqrtf(-expm1f(2.f * log_a)) * sigmoid_f(ri[tt]) * u_s[tt * ld + o];
     }
+  }
+}
+
+// The same for few tokens (single tokens of a batch): a warp an output channel, its lanes spread over the
+// part's inputs, so that a step's few rows still give a block to every SM and every weight is read once, in
+// whole lines.  Weights here lie as stored, [part][out][in].  grid (channels / 8, token tiles of 8).
+constexpr int kLruFewTokens = 8;
+__global__ void __launch_bounds__(256)
+lru_gates_few_kernel(float* __restrict__ a_out, float* __restrict__ x_out, const float* __restrict__ u, int u_stride,
+                     const float* __restrict__ w_a, const float* __restrict__ b_a, const float* __restrict__ w_i,
+                     const float* __restrict__ b_i, const float* __restrict__ lam, float rate, int n_tokens, int parts,
+                     int size) {
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * 8 + warp, R = parts * size;
+  if (c >= R) return;
+  const int p = c / size;
+  const float* wa = w_a + (size_t)c * size;     // row c of the part's matrix: [out][in]
+  const float* wi = w_i + (size_t)c * size;
+  const int t0 = blockIdx.y * kLruFewTokens;
+  const int nt = min(kLruFewTokens, n_tokens - t0);
+  float ra[kLruFewTokens], ri[kLruFewTokens];
+#pragma unroll
+  for (int tt = 0; tt < kLruFewTokens; ++tt) ra[tt] = ri[tt] = 0.f;
+  float va[8], vi[8];                           // the weights do not depend on the kernel before: fetch, then wait
+  const int chunks = (size + 255) / 256;
+  for (int ch = 0; ch < chunks; ++ch) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = ch * 256 + j * 32 + lane;
+      va[j] = r < size ? wa[r] : 0.f;
+      vi[j] = r < size ? wi[r] : 0.f;
+    }
+    if (ch == 0) pdl_wait();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = ch * 256 + j * 32 + lane;
+      if (r < size) {
+#pragma unroll
+        for (int tt = 0; tt < kLruFewTokens; ++tt) {
+          const float x = tt < nt ? u[(size_t)(t0 + tt) * u_stride + p * size + r] : 0.f;
+          ra[tt] = fmaf(va[j], x, ra[tt]);
+          ri[tt] = fmaf(vi[j], x, ri[tt]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int tt = 0; tt < kLruFewTokens; ++tt) { ra[tt] = warp_sum(ra[tt]); ri[tt] = warp_sum(ri[tt]); }
+  if (lane < nt) {
+    float sa = 0.f, si = 0.f;
+#pragma unroll
+    for (int tt = 0; tt < kLruFewTokens; ++tt) if (tt == lane) { sa = ra[tt]; si = ri[tt]; }
+    const float log_a = -rate * softplus_f(lam[c]) * sigmoid_f(sa + (b_a ? b_a[c] : 0.f));
+    const size_t at = (size_t)(t0 + lane) * R + c;
+    a_out[at] = expf(log_a);
+    x_out[at] = sqrtf(-expm1f(2.f * log_a)) * sigmoid_f(si + (b_i ? b_i[c] : 0.f)) * u[(size_t)(t0 + lane) * u_stride + c];
   }
 }
 
@@ -207,6 +276,70 @@ lru_scan_kernel(T* __restrict__ out, const float* __restrict__ a, const float* _
     out[row * channels + c] = from_f<T>(S * g);
   }
   if (write_state) *sp = S;
+}
+
+// The same recurrence for prompts: 8 warps take 8 neighbouring stretches of 32 tokens of 32 channels (a lane
+// a channel).  The map S -> a S + x of a stretch composes to S -> A S + B; each warp forms its stretch's (A, B)
+// from zero, the eight meet in shared memory, every warp applies the stretches before its own to the state it
+// was handed, and then walks its tokens again (they are still in L1 / L2) with the true state.  The chain from
+// token to token is a quarter as long as one thread a channel, with eight times the loads in flight.
+constexpr int kLruWarps = 8, kLruStretch = 32;
+template <typename T>
+__global__ void __launch_bounds__(kLruWarps * 32)
+lru_scan_wide_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ x,
+                     const float* __restrict__ side, int side_stride, int side_col,
+                     const float* __restrict__ side_bias, float* __restrict__ state, size_t slot_stride,
+                     const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
+                     const int* __restrict__ token_slot, int channels, int write_state) {
+  __shared__ float A_s[kLruWarps][32], B_s[kLruWarps][32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x, c = blockIdx.y * 32 + lane;
+  const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+  if (n <= 0) return;
+  const bool live = c < channels;
+  if (positions[start] < 0) {                   // rows of a finished sequence: zeros, the state untouched
+    if (live)
+      for (int i = warp; i < n; i += kLruWarps) out[(size_t)(start + i) * channels + c] = from_f<T>(0.f);
+    return;
+  }
+  float* sp = state + (size_t)token_slot[start] * slot_stride + c;
+  float S0 = live ? *sp : 0.f;
+  const float sb = (side_bias && live) ? side_bias[c] : 0.f;
+  for (int base = 0; base < n; base += kLruWarps * kLruStretch) {
+    const int lo = base + warp * kLruStretch, hi = min(lo + kLruStretch, n);
+    float A = 1.f, B = 0.f;
+    if (live) {
+#pragma unroll 8
+      for (int i = lo; i < hi; ++i) {
+        const size_t at = (size_t)(start + i) * channels + c;
+        const float av = a[at];
+        A *= av;
+        B = fmaf(av, B, x[at]);
+      }
+    }
+    A_s[warp][lane] = A;
+    B_s[warp][lane] = B;
+    __syncthreads();
+    float S = S0;
+    for (int w = 0; w < warp; ++w) S = fmaf(A_s[w][lane], S, B_s[w][lane]);
+    if (live) {
+#pragma unroll 4
+      for (int i = lo; i < hi; ++i) {
+        const size_t row = (size_t)(start + i);
+        S = fmaf(a[row * channels + c], S, x[row * channels + c]);
+        const float z = side[row * side_stride + side_col + c] + sb;
+        const float g = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        out[row * channels + c] = from_f<T>(S * g);
+      }
+    }
+    float all = S0;
+    for (int w = 0; w < kLruWarps; ++w) all = fmaf(A_s[w][lane], all, B_s[w][lane]);
+    S0 = all;
+    __syncthreads();                            // before the next pass overwrites A_s, B_s
+  }
+  if (write_state && live && warp == 0) *sp = S0;
 }
 
 // a[t, h] = exp(-exp(a_log[h]) dt), b[t, h] = dt, dt = softplus(proj[t, col0 + h] + dt_bias[h]).
@@ -566,14 +699,20 @@ EK_EXPORT int ek_conv_act(float* out, int out_stride, const float* proj, int pro
 }
 
 // Both gates of the gated linear recurrence and what enters it: a[t, c] and x[t, c] (see lru_gates_kernel).
-// u [T, R] 32-bit rows `u_stride` apart; w_a, w_i [parts][in][out] (transposed at load); R = parts * size.
+// u [T, R] 32-bit rows `u_stride` apart; w_a, w_i [parts][in][out] (transposed at load); w_a_rows, w_i_rows
+// (nullable) the same matrices as stored, [parts][out][in], for steps of few tokens; R = parts * size.
 EK_EXPORT int ek_lru_gates(float* a, float* x, const float* u, int u_stride, const float* w_a, const float* b_a,
-                           const float* w_i, const float* b_i, const float* lam, float rate, int n_tokens,
-                           int parts, int size, cudaStream_t stream) {
+                           const float* w_i, const float* b_i, const float* w_a_rows, const float* w_i_rows,
+                           const float* lam, float rate, int n_tokens, int parts, int size, cudaStream_t stream) {
   using namespace ek;
   if (n_tokens <= 0) return 0;
   if (parts <= 0 || size <= 0 || parts > 65535) return EK_ERR_ARG;
-  const size_t smem = (size_t)kLruTokens * size * sizeof(float);
+  if (n_tokens <= 64 && w_a_rows && w_i_rows) {          // few tokens: a warp an output channel, weights as stored
+    dim3 grid((parts * size + 7) / 8, (n_tokens + kLruFewTokens - 1) / kLruFewTokens);
+    return (int)launch_pdl(lru_gates_few_kernel, grid, dim3(256), 0, stream, a, x, u, u_stride, w_a_rows, b_a,
+                           w_i_rows, b_i, lam, rate, n_tokens, parts, size);
+  }
+  const size_t smem = (size_t)kLruTokens * ((size + 3) & ~3) * sizeof(float);
   if (smem > 200 * 1024) return EK_ERR_ARG;
   if (smem > 40 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(lru_gates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -589,9 +728,17 @@ EK_EXPORT int ek_lru_gates(float* a, float* x, const float* u, int u_stride, con
                                      int side_stride, int side_col, const float* side_bias, float* state,    \
                                      long long slot_stride, const int* cu_seqlens, const int* positions,     \
                                      const int* token_slot, int n_seqs, int channels, int write_state,       \
-                                     cudaStream_t stream) {                                                  \
+                                     int max_new, cudaStream_t stream) {                                     \
     if (n_seqs <= 0) return 0;                                                                               \
     if (channels <= 0) return EK_ERR_ARG;                                                                    \
+    if (max_new > 16) {              /* some sequence brings a stretch of tokens: the form for prompts */    \
+      dim3 wide(n_seqs, (channels + 31) / 32);                                                               \
+      if (wide.y > 65535) return EK_ERR_ARG;                                                                 \
+      return (int)ek::launch_pdl(ek::lru_scan_wide_kernel<T>, wide, dim3(ek::kLruWarps * 32), 0, stream,     \
+                                 (T*)out, a, x, side, side_stride, side_col, side_bias, state,               \
+                                 (size_t)slot_stride, cu_seqlens, positions, token_slot, channels,           \
+                                 write_state);                                                               \
+    }                                                                                                        \
     dim3 grid(n_seqs, (channels + 127) / 128);                                                               \
     if (grid.y > 65535) return EK_ERR_ARG;                                                                   \
     return (int)ek::launch_pdl(ek::lru_scan_kernel<T>, grid, dim3(128), 0, stream, (T*)out, a, x, side,      \

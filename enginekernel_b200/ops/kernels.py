@@ -567,6 +567,35 @@ _attn_decode_bf16 = Function("attention_decode_bf16", "ek_attention_decode_bf16"
                               c_float, c_int, c_int, c_int, _P, _P, c_float, _P, c_int, _P, c_int, _P])
 
 
+_attn_decode_cross = Function("attention_decode_bf16", "ek_attention_decode_cross_bf16",
+                              [_P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                               c_float, c_int, c_int, c_int, _P, _P, c_int, _P])
+
+
+def attention_decode_cross_bf16(parts, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table, n_q_heads,
+                                n_kv_heads, head_dim, scale, window=None, n_splits=1, keys_per_split=0, part_acc=None,
+                                part_ml=None, keep_first=0):
+    """:func:`attention_generic_cross` for single tokens in bfloat16 on the register-streaming decode kernel:
+    a block takes a token, a key head's group and ONE value head, for every pair of the two; split buffers
+    hold NQ * NKV rows a token."""
+    _need_cuda(parts, q, positions, token_slot, k_pages, v_pages, block_table, part_acc, part_ml)
+    _need(attention_decode_supported(q.dtype, head_dim), "attention_decode_cross_bf16: head sizes in steps of 32")
+    _need(q.dtype == k_pages.dtype == torch.bfloat16 and parts.dtype == torch.float32 and parts.is_contiguous()
+          and parts.numel() >= n_tokens * n_q_heads * n_kv_heads * head_dim and q.stride(-1) == 1
+          and q.stride(0) % 8 == 0, "attention_decode_cross_bf16: parts [T, NQ, NKV, D] in 32-bit")
+    if n_splits > 1:
+        _need(part_acc is not None and part_ml is not None
+              and part_acc.numel() >= n_tokens * n_q_heads * n_kv_heads * n_splits * head_dim
+              and part_ml.numel() >= n_tokens * n_q_heads * n_kv_heads * n_splits * 2, "attention: split buffers")
+    _attention_cost(q, n_tokens, positions, n_q_heads * n_kv_heads, n_kv_heads, head_dim, window, False)
+    _attn_decode_cross(_ptr(parts), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot), _ptr(k_pages),
+                       _ptr(v_pages), _ptr(block_table), block_table.stride(0), n_tokens, n_q_heads, n_kv_heads,
+                       head_dim, float(scale), int(window or 0), n_splits, keys_per_split, _ptr(part_acc),
+                       _ptr(part_ml), int(keep_first or 0), _stream())
+    if n_splits > 1:
+        count_extra_launches()
+
+
 def _gate_args(gate, q, n_q_heads):
     """(pointer, row stride) of the optional per-head gate, checked."""
     _need(gate is None or (gate.is_cuda and gate.dtype == q.dtype and gate.stride(-1) == 1
@@ -697,6 +726,26 @@ _attn_prefill_tc = Function("attention_prefill_tc", "ek_attention_prefill_tc",
                              c_int, c_int, c_float, c_int, _P, c_float, _P])
 _attn_prefill_tiles = Function("attention_prefill_tc", "ek_attention_prefill_tiles",
                                [_P, c_int, _P, _P, _P, c_int, c_int, c_int, _P])
+_attn_prefill_cross = Function("attention_prefill_bf16", "ek_attention_prefill_cross_bf16",
+                               [_P, _P, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int,
+                                c_float, c_int, c_int, _P])
+
+
+def attention_prefill_cross_bf16(parts, q, n_tokens, positions, token_slot, cu_seqlens, n_seqs, k_pages, v_pages,
+                                 block_table, n_q_heads, n_kv_heads, head_dim, scale, window=None, keep_first=0):
+    """:func:`attention_generic_cross` for prompts in bfloat16 on the ``mma.sync`` kernel: a block takes a
+    tile of (token, head of the group) rows against one key head and ONE value head, for every pair of the two."""
+    _need_cuda(parts, q, positions, token_slot, cu_seqlens, k_pages, v_pages, block_table)
+    _need(attention_prefill_supported(q.dtype, head_dim, n_q_heads, n_kv_heads), "attention_prefill_cross_bf16: sizes")
+    _need(q.dtype == k_pages.dtype == torch.bfloat16 and parts.dtype == torch.float32 and parts.is_contiguous()
+          and parts.numel() >= n_tokens * n_q_heads * n_kv_heads * head_dim and q.stride(-1) == 1
+          and q.stride(0) % 8 == 0, "attention_prefill_cross_bf16: parts [T, NQ, NKV, D] in 32-bit")
+    _attention_cost(q, n_tokens, positions, n_q_heads * n_kv_heads, n_kv_heads, head_dim, window, True)
+    _attn_prefill_cross(_ptr(parts), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot), _ptr(cu_seqlens), n_seqs,
+                        n_tokens, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0), n_q_heads,
+                        n_kv_heads, head_dim, float(scale), int(window or 0), int(keep_first or 0), _stream())
+
+
 PREFILL_TC_ROWS = 128       # (token, query head of a group) rows a block of attention_prefill_tc owns
 PREFILL_TC_MAX_SEQS = 1024
 
@@ -1489,9 +1538,9 @@ _conv_act = Function("recurrent", "ek_conv_act",
                      [_P, c_int, _P, c_int, c_int, _P, _P, _P, c_int, _P, c_longlong, c_longlong, _P, _P, c_int, c_int,
                       c_int, _P])
 _lru_gates = Function("recurrent", "ek_lru_gates",
-                      [_P, _P, _P, c_int, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, _P])
+                      [_P, _P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, _P])
 _lru_scan = _per_dtype("recurrent", "ek_lru_scan",
-                       [_P, _P, _P, _P, c_int, c_int, _P, _P, c_longlong, _P, _P, _P, c_int, c_int, c_int, _P])
+                       [_P, _P, _P, _P, c_int, c_int, _P, _P, c_longlong, _P, _P, _P, c_int, c_int, c_int, c_int, _P])
 
 
 def conv_act(out, proj, col0, conv_w, conv_b, state, tail_offset, positions, token_slot, n_tokens, channels, taps,
@@ -1511,26 +1560,31 @@ def conv_act(out, proj, col0, conv_w, conv_b, state, tail_offset, positions, tok
               _ptr(token_slot), n_tokens, channels, taps, _stream())
 
 
-def lru_gates(a, x, u, w_a, b_a, w_i, b_i, lam, rate, n_tokens, parts, size):
+def lru_gates(a, x, u, w_a, b_a, w_i, b_i, lam, rate, n_tokens, parts, size, w_a_rows=None, w_i_rows=None):
     """Gates of a gated linear recurrence over ``parts * size`` channels: r = sigmoid(W_a[p] u_p + b_a),
     i = sigmoid(W_i[p] u_p + b_i) per part p; a = exp(-rate * r * softplus(lam)), x = sqrt(1 - a^2) * i * u.
-    ``w_a``, ``w_i`` [parts, in, out] (transposed), everything 32-bit."""
-    _need_cuda(a, x, u, w_a, b_a, w_i, b_i, lam)
-    _need_f32("lru_gates", a, x, u, w_a, b_a, w_i, b_i, lam)
+    ``w_a``, ``w_i`` [parts, in, out] (transposed), everything 32-bit.  ``w_a_rows``, ``w_i_rows``: the same
+    matrices [parts, out, in]; with them steps of at most 64 tokens run a warp per output channel."""
+    _need_cuda(a, x, u, w_a, b_a, w_i, b_i, lam, w_a_rows, w_i_rows)
+    _need_f32("lru_gates", a, x, u, w_a, b_a, w_i, b_i, lam, w_a_rows, w_i_rows)
+    for t in (w_a_rows, w_i_rows):
+        _need(t is None or (t.is_contiguous() and tuple(t.shape) == (parts, size, size)), "lru_gates: rows [parts, size, size]")
     width = parts * size
     _need(a.is_contiguous() and x.is_contiguous() and a.shape[-1] == width == x.shape[-1] and u.shape[-1] >= width
           and w_a.is_contiguous() and w_i.is_contiguous() and tuple(w_a.shape) == (parts, size, size) == tuple(w_i.shape)
           and lam.numel() == width, "lru_gates: a, x [T, parts * size]; weights [parts, size, size]")
     if lib.recording():
         lib.annotate(bytes=4 * (3 * n_tokens * width + 2 * parts * size * size), flops=4 * n_tokens * width * size)
-    _lru_gates(_ptr(a), _ptr(x), _ptr(u), u.stride(0), _ptr(w_a), _ptr(b_a), _ptr(w_i), _ptr(b_i), _ptr(lam),
-               float(rate), n_tokens, parts, size, _stream())
+    _lru_gates(_ptr(a), _ptr(x), _ptr(u), u.stride(0), _ptr(w_a), _ptr(b_a), _ptr(w_i), _ptr(b_i), _ptr(w_a_rows),
+               _ptr(w_i_rows), _ptr(lam), float(rate), n_tokens, parts, size, _stream())
 
 
 def lru_scan(out, a, x, side, side_col, side_bias, state, cu_seqlens, positions, token_slot, n_seqs, channels,
-             write_state=True, n_tokens=0):
+             write_state=True, n_tokens=0, max_new=1):
     """S_t = a_t S_(t-1) + x_t per channel over every sequence's tokens, S (the first ``channels`` values of a
-    slot's state) read and written back; out[t, c] = S_t * gelu_tanh(side[t, side_col + c] + side_bias[c])."""
+    slot's state) read and written back; out[t, c] = S_t * gelu_tanh(side[t, side_col + c] + side_bias[c]).
+    ``max_new``: the longest run of tokens a sequence brings (above 16 the kernel cuts runs into stretches that
+    eight warps take side by side)."""
     _need_cuda(out, a, x, side, side_bias, state, cu_seqlens, positions, token_slot)
     _need_f32("lru_scan", a, x, side, side_bias, state)
     _need(out.is_contiguous() and a.is_contiguous() and x.is_contiguous() and out.shape[-1] == channels
@@ -1540,7 +1594,7 @@ def lru_scan(out, a, x, side, side_col, side_bias, state, cu_seqlens, positions,
         lib.annotate(bytes=n_tokens * channels * (12 + out.element_size()) + 8 * n_seqs * channels)
     _lru_scan[out.dtype](_ptr(out), _ptr(a), _ptr(x), _ptr(side), side.stride(0), side_col, _ptr(side_bias),
                          _ptr(state), state.stride(0), _ptr(cu_seqlens), _ptr(positions), _ptr(token_slot), n_seqs,
-                         channels, 1 if write_state else 0, _stream())
+                         channels, 1 if write_state else 0, int(max_new), _stream())
 
 
 def conv_tail(state, tail_offset, proj, col0, cu_seqlens, positions, token_slot, n_seqs, channels, taps):

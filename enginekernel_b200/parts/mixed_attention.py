@@ -15,8 +15,8 @@ Because the mix is linear, o_a = sum_b mix[a, b] A[b, c(a)] with A[b, c] = head 
 the values of key/value head c; the attention kernel writes A (32-bit) and a second kernel forms the sums,
 applies the gate and rounds.  Scores, softmax, A and the sums are 32-bit.
 
-The kernels and the cache see heads of one size, max(d, e) rounded up to 8 values, the shorter ones padded with
-zeros (zero weight rows); the norms take their means over the true sizes.  The pairing of neighbours is
+The kernels and the cache see heads of one size, max(d, e) rounded up to 8 values (32 in bfloat16), the shorter
+ones padded with zeros (zero weight rows); the norms take their means over the true sizes.  The pairing of neighbours is
 turned into the half-split pairing the rotation kernels use by reordering the rows of W_q and W_k (and their
 biases and gains) once at load: scores do not change when queries and keys are permuted alike.
 
@@ -70,7 +70,9 @@ class MixedHeadAttention(Mixer):
             raise ValueError("mixed_head_attention: num_heads must be a multiple of num_kv_heads")
         if self.keep_first and not self.window:
             raise ValueError("mixed_head_attention: keep_first needs a window")
-        self.padded_dim = -(-max(self.head_dim, self.value_dim) // 8) * 8
+        # (in bfloat16 a multiple of 32, which both 16-bit attention kernels take)
+        unit = 32 if dtype == torch.bfloat16 else 8
+        self.padded_dim = -(-max(self.head_dim, self.value_dim) // unit) * unit
         kernels.check_head_dim(self.padded_dim)
         pos = spec.params.get("position")
         self.position = lookup_part("position", pos.kind)(pos, dtype, device) if pos else None
@@ -132,7 +134,30 @@ class MixedHeadAttention(Mixer):
             write_kv=writes_cache, q_bias=self.q_bias, k_bias=self.k_bias, v_bias=self.v_bias,
             value_unit_eps=self.eps, value_dim=self.value_dim)
         parts = ctx.workspace.get("mixed_parts", (t, nh, g, big), torch.float32)
+        out = ctx.workspace.get("attn_out", (t, nh * self.value_dim), self.dtype)
+        if not ctx.is_decode and kernels.attention_prefill_supported(self.dtype, big, nh, g):
+            kernels.attention_prefill_cross_bf16(parts, rows, t, ctx.positions, ctx.token_slot, ctx.cu_seqlens,
+                                                 ctx.n_seqs, entry.k_pages, entry.v_pages, entry.block_table, nh, g,
+                                                 big, self.scale, self.window, keep_first=self.keep_first)
+            kernels.mix_heads(out, parts, self.mix, ctx.positions, t, nh, g, big, self.value_dim,
+                              gate=rows[:, self.gate_col:])
+            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t)
         visible = min(ctx.max_context, self.window + self.keep_first) if self.window else ctx.max_context
+        if ctx.is_decode and kernels.attention_decode_supported(self.dtype, big):
+            # blocks = tokens x key heads (x 16-row blocks of the group) x value heads, three fit an SM: every
+            # token's own window is cut so that the blocks about fill the machine, never finer than two pages a split
+            blocks = t * g * -(-(nh // g) // 16) * g
+            splits = max(1, min(3 * kernels.sm_count(self.device) // blocks, -(-visible // 128)))
+            acc = ml = None
+            if splits > 1:
+                acc = ctx.workspace.get("attn_part_acc", (t, nh * g, splits, big), torch.float32)
+                ml = ctx.workspace.get("attn_part_ml", (t, nh * g, splits, 2), torch.float32)
+            kernels.attention_decode_cross_bf16(parts, rows, t, ctx.positions, ctx.token_slot, entry.k_pages,
+                                                entry.v_pages, entry.block_table, nh, g, big, self.scale, self.window,
+                                                splits, 0, acc, ml, keep_first=self.keep_first)
+            kernels.mix_heads(out, parts, self.mix, ctx.positions, t, nh, g, big, self.value_dim,
+                              gate=rows[:, self.gate_col:])
+            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t)
         splits, per_split, acc, ml = 1, 0, None, None
         blocks = t * nh * g
         if blocks < 2 * kernels.sm_count(self.device) and visible > 512:
@@ -146,7 +171,6 @@ class MixedHeadAttention(Mixer):
         kernels.attention_generic_cross(parts, rows, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
                                         entry.block_table, nh, g, big, self.scale, self.window, splits, per_split,
                                         acc, ml, keep_first=self.keep_first)
-        out = ctx.workspace.get("attn_out", (t, nh * self.value_dim), self.dtype)
         kernels.mix_heads(out, parts, self.mix, ctx.positions, t, nh, g, big, self.value_dim,
                           gate=rows[:, self.gate_col:])
         return linear(out, self.w_o, ctx, "attn_proj", n_rows=t)

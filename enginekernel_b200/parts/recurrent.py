@@ -227,7 +227,7 @@ class GatedLinearRecurrence(Mixer):
             raise ValueError("gated_linear_recurrence: the convolution has at least one tap")
         self.size = self.width // self.blocks
         self.w_in = self.w_o = self.y_bias = self.x_bias = self.conv_w = self.conv_b = None
-        self.w_a = self.w_i = self.b_a = self.b_i = self.lam = None
+        self.w_a = self.w_i = self.w_a_rows = self.w_i_rows = self.b_a = self.b_i = self.lam = None
 
     def cache_spec(self):
         return CacheSpec("state", shape=(-(-(self.width * self.taps) // 4) * 4,))
@@ -243,6 +243,9 @@ class GatedLinearRecurrence(Mixer):
         # [part][in][out]: neighbouring threads of the gate kernel own neighbouring outputs
         self.w_a = tensors[w["a_gate"]].to(f32).transpose(1, 2).contiguous()
         self.w_i = tensors[w["i_gate"]].to(f32).transpose(1, 2).contiguous()
+        # and as stored, [part][out][in], for steps of few tokens (a warp reads an output's row)
+        self.w_a_rows = tensors[w["a_gate"]].to(f32).contiguous()
+        self.w_i_rows = tensors[w["i_gate"]].to(f32).contiguous()
         self.b_a = tensors[w["a_gate_bias"]].to(f32).reshape(-1).contiguous()
         self.b_i = tensors[w["i_gate_bias"]].to(f32).reshape(-1).contiguous()
         self.lam = tensors[w["lam"]].to(f32).contiguous()
@@ -261,8 +264,14 @@ class GatedLinearRecurrence(Mixer):
         a = ws.get("lru_a", (t, r), f32)
         xin = ws.get("lru_x", (t, r), f32)
         kernels.lru_gates(a, xin, u, self.w_a, self.b_a, self.w_i, self.b_i, self.lam, self.rate, t, self.blocks,
-                          self.size)
+                          self.size, w_a_rows=self.w_a_rows, w_i_rows=self.w_i_rows)
         y = ws.get("attn_out", (t, r), self.dtype)
         kernels.lru_scan(y, a, xin, proj, 0, self.y_bias, state, ctx.cu_seqlens, ctx.positions, ctx.token_slot,
-                         ctx.n_seqs, r, write_state=writes_cache, n_tokens=t)
+                         ctx.n_seqs, r, write_state=writes_cache, n_tokens=t, max_new=ctx.max_new)
         return linear(y, self.w_o, ctx, "attn_proj", n_rows=t)
+
+    def bytes_read_per_step(self, n_tokens):
+        # (the gates' matrices are held in two layouts; a step reads one of them)
+        read = (self.w_in, self.w_o, self.w_a, self.w_i, self.y_bias, self.x_bias, self.conv_w, self.conv_b, self.b_a,
+                self.b_i, self.lam)
+        return sum(t.numel() * t.element_size() for t in read)

@@ -100,9 +100,17 @@ def test_bias_with_activation_and_cast_into_columns(dtype):
             out = torch.empty(7, 30, dtype=dtype, device=DEV)
             k.bias_act(out, src, bias, act, col0=11)
             assert rel(out, f(src.double()[:, 11:41] + bias.double())) <= TOL[dtype]
+    wide, bias4 = rnd(5, 96, seed=3, scale=2.0), rnd(64, seed=4)             # sizes the four-values-a-thread form takes
+    for src in (wide, wide.to(dtype)):
+        out = torch.empty(5, 64, dtype=dtype, device=DEV)
+        k.bias_act(out, src, bias4, "gelu_tanh", col0=16)
+        assert rel(out, plain.gelu_tanh(src.double()[:, 16:80] + bias4.double())) <= TOL[dtype]
     dst = torch.zeros(7, 64, dtype=dtype, device=DEV)
     k.cast_columns(dst, 9, x32, 7)
     assert torch.equal(dst[:, 9:59], x32.to(dtype)) and dst[:, :9].abs().sum() == 0 and dst[:, 59:].abs().sum() == 0
+    dst = torch.zeros(5, 128, dtype=dtype, device=DEV)
+    k.cast_columns(dst, 24, wide, 5)
+    assert torch.equal(dst[:, 24:120], wide.to(dtype)) and dst[:, :24].abs().sum() == 0 and dst[:, 120:].abs().sum() == 0
 
 
 @pytest.mark.parametrize("channels,taps", [(30, 4), (7, 1), (300, 2), (64, 3)])
@@ -145,11 +153,14 @@ def test_gates_of_the_linear_recurrence(parts, size):
     uu = u[:, :width].double().cpu()
     r, i = plain.rglru_gates(uu, w, "", parts)
     log_a = -8.0 * r * plain.softplus(lam.double().cpu())
-    a, x = torch.empty(n, width, device=DEV), torch.empty(n, width, device=DEV)
-    k.lru_gates(a, x, u, wa.transpose(1, 2).contiguous(), ba.reshape(-1), wi.transpose(1, 2).contiguous(), bi.reshape(-1),
-                lam, 8.0, n, parts, size)
-    assert rel(a, torch.exp(log_a)) <= 1e-5
-    assert rel(x, torch.sqrt(1 - torch.exp(2 * log_a)) * i * uu) <= 1e-5
+    wat, wit = wa.transpose(1, 2).contiguous(), wi.transpose(1, 2).contiguous()
+    # a tile of tokens a block (prompts), and a warp an output channel (steps of few tokens, weights as stored)
+    for rows in ({}, {"w_a_rows": wa.contiguous(), "w_i_rows": wi.contiguous()}):
+        for m in (n, 3, 1):
+            a, x = torch.empty(m, width, device=DEV), torch.empty(m, width, device=DEV)
+            k.lru_gates(a, x, u[:m], wat, ba.reshape(-1), wit, bi.reshape(-1), lam, 8.0, m, parts, size, **rows)
+            assert rel(a, torch.exp(log_a)[:m]) <= 1e-5
+            assert rel(x, (torch.sqrt(1 - torch.exp(2 * log_a)) * i * uu)[:m]) <= 1e-5
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -157,7 +168,7 @@ def test_gates_of_the_linear_recurrence(parts, size):
 def test_scan_of_the_linear_recurrence_from_a_carried_state(dtype, channels):
     """Three unequal sequences at once, then each continued from its state in slots that others used before."""
     k = K()
-    lens, slots = [9, 1, 30], [2, 0, 3]
+    lens, slots = [9, 1, 30 if channels != 128 else 700], [2, 0, 3]        # (700: several passes of eight stretches)
     n = sum(lens)
     a = torch.rand(2 * n, channels, generator=torch.Generator().manual_seed(1)).to(DEV) * 0.6 + 0.4
     x, side = rnd(2 * n, channels, seed=2), rnd(2 * n, channels + 4, seed=3)
@@ -183,7 +194,8 @@ def test_scan_of_the_linear_recurrence_from_a_carried_state(dtype, channels):
         pos = [half * ln + j for ln in lens for j in range(ln)]
         out = torch.empty(n, channels, dtype=dtype, device=DEV)
         k.lru_scan(out, a[half * n:(half + 1) * n].contiguous(), x[half * n:(half + 1) * n].contiguous(),
-                   side[half * n:(half + 1) * n], 2, sb, state, i32(cu), i32(pos), i32(tok_slots), 3, channels)
+                   side[half * n:(half + 1) * n], 2, sb, state, i32(cu), i32(pos), i32(tok_slots), 3, channels,
+                   max_new=max(lens))
         for j, ln in enumerate(lens):
             assert rel(out[cu[j]:cu[j + 1]], want[j][half * ln:(half + 1) * ln]) <= TOL[dtype], (half, j)
     assert torch.equal(state[1], rnd(4, channels + 6, seed=5)[1])             # a slot nobody holds is not touched
@@ -303,6 +315,46 @@ def test_heads_that_share_their_weights_behind_a_window_with_kept_first_tokens(d
         want = mc.sum(1, keepdim=True).double() * vc[j, :, :e].double().repeat_interleave(nq // nkv, 0)
         hit = rel(out[0].view(nq, e), want) <= 2e-2
         assert hit == seen, (j, seen)
+
+
+@pytest.mark.parametrize("d,nq,nkv", [(64, 4, 2), (96, 6, 1), (128, 8, 4)])
+@pytest.mark.parametrize("window,keep,length", [(9, 3, 40), (70, 5, 300), (64, 64, 200), (3, 1, 700), (130, 70, 400)])
+def test_the_16_bit_prompt_and_decode_kernels_apply_every_heads_weights_to_every_value_head(d, nq, nkv, window, keep, length):
+    """Both 16-bit kernels against the general one, which the test above holds against the plain rule: a prompt
+    whole and cut behind a cached prefix, single tokens with the keys whole and split."""
+    k = K()
+    dtype, scale = torch.bfloat16, 0.3
+    pages = Pages(2, length, nkv, d, dtype, seed=length)
+    keys, values = rnd(length, nkv, d, dtype=dtype, seed=1), rnd(length, nkv, d, dtype=dtype, seed=2)
+    pages.fill(1, keys, values)
+    q = rnd(length, nq * d + 8, dtype=dtype, seed=3)
+    pos, slots = i32(list(range(length))), i32([1] * length)
+    want = torch.empty(length, nq, nkv, d, device=DEV)
+    k.attention_generic_cross(want, q, length, pos, slots, pages.k, pages.v, pages.table, nq, nkv, d, scale, window,
+                              keep_first=keep)
+    got = torch.full((length, nq, nkv, d), 7.0, device=DEV)
+    k.attention_prefill_cross_bf16(got, q, length, pos, slots, i32([0, length]), 1, pages.k, pages.v, pages.table, nq, nkv,
+                                   d, scale, window, keep_first=keep)
+    assert rel(got, want) <= 2e-2
+    cut = length // 3 + 1                                                   # the rest of the prompt behind a cached part
+    got2 = torch.full((length - cut, nq, nkv, d), 7.0, device=DEV)
+    k.attention_prefill_cross_bf16(got2, q[cut:], length - cut, pos[cut:].contiguous(), slots[cut:].contiguous(),
+                                   i32([0, length - cut]), 1, pages.k, pages.v, pages.table, nq, nkv, d, scale, window,
+                                   keep_first=keep)
+    assert rel(got2, want[cut:]) <= 2e-2
+    picks = sorted({0, 1, keep, window - 1, window, window + keep, 63, 64, length - 1} & set(range(length)))
+    rows = q[picks].contiguous()
+    for splits in (1, 3):
+        acc = torch.empty(len(picks), nq * nkv, splits, d, device=DEV) if splits > 1 else None
+        ml = torch.empty(len(picks), nq * nkv, splits, 2, device=DEV) if splits > 1 else None
+        got3 = torch.full((len(picks), nq, nkv, d), 7.0, device=DEV)
+        k.attention_decode_cross_bf16(got3, rows, len(picks), i32(picks), i32([1] * len(picks)), pages.k, pages.v, pages.table,
+                                      nq, nkv, d, scale, window, splits, 0, acc, ml, keep_first=keep)
+        assert rel(got3, want[picks]) <= 2e-2, splits
+    dead = torch.full((2, nq, nkv, d), 7.0, device=DEV)                     # rows of finished sequences give zeros
+    k.attention_decode_cross_bf16(dead, rows[:2], 2, i32([-1, -1]), i32([1, 1]), pages.k, pages.v, pages.table, nq, nkv, d,
+                                  scale, window, keep_first=keep)
+    assert dead.abs().sum() == 0
 
 
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 16, 24), (2, 2, 64, 32), (6, 1, 12, 20), (3, 3, 128, 64)])
