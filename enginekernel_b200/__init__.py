@@ -1,7 +1,7 @@
 """enginekernel_b200: a small model library with generation for one NVIDIA B200.
 
 Everything between a request's tokens and its next token for the Qwen3 dense decoder and the Lopazen,
-Susalorn and Bolelix decoders: typed configuration and registry, safetensors weights, layers put together from parts,
+Susalorn, Bolelix and Musavik decoders: typed configuration and registry, safetensors weights, layers put together from parts,
 a paged cache with a slot per sequence, one step function, a generation loop, sampling,
 hand-written CUDA kernels for sm_100a, a true 32-bit path and a trace-replay tool.
 """

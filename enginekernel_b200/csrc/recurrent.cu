@@ -278,12 +278,14 @@ lru_scan_kernel(T* __restrict__ out, const float* __restrict__ a, const float* _
   if (write_state) *sp = S;
 }
 
-// The same recurrence for prompts: 8 warps take 8 neighbouring stretches of 32 tokens of 32 channels (a lane
-// a channel).  The map S -> a S + x of a stretch composes to S -> A S + B; each warp forms its stretch's (A, B)
-// from zero, the eight meet in shared memory, every warp applies the stretches before its own to the state it
-// was handed, and then walks its tokens again (they are still in L1 / L2) with the true state.  The chain from
-// token to token is a quarter as long as one thread a channel, with eight times the loads in flight.
-constexpr int kLruWarps = 8, kLruStretch = 32;
+// The same recurrence for prompts: a block of 32 warps takes 16 channels and walks a sequence 1,024 tokens a
+// pass - 64 neighbouring stretches of 16 tokens, two to a warp (a half-warp a stretch, a lane a channel).  The map
+// S -> a S + x of a stretch composes to S -> A S + B; every half-warp forms its stretch's (A, B) from zero, the 64
+// meet in shared memory, every half-warp applies the stretches before its own to the state the pass was handed,
+// and then walks its tokens again (they are still in L1 / L2) with the true state.  The chain from token to
+// token is 16 long instead of the whole run, and a prompt of one sequence still fills the machine's schedulers.
+constexpr int kLruWarps = 32, kLruStretch = 16, kLruLanes = 16;
+constexpr int kLruSubs = kLruWarps * 32 / kLruLanes;          // stretches a pass
 template <typename T>
 __global__ void __launch_bounds__(kLruWarps * 32)
 lru_scan_wide_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ x,
@@ -291,24 +293,24 @@ lru_scan_wide_kernel(T* __restrict__ out, const float* __restrict__ a, const flo
                      const float* __restrict__ side_bias, float* __restrict__ state, size_t slot_stride,
                      const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
                      const int* __restrict__ token_slot, int channels, int write_state) {
-  __shared__ float A_s[kLruWarps][32], B_s[kLruWarps][32];
+  __shared__ float A_s[kLruSubs][kLruLanes], B_s[kLruSubs][kLruLanes];
   pdl_launch_dependents();
   pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.x, c = blockIdx.y * 32 + lane;
+  const int sub = threadIdx.x / kLruLanes, cl = threadIdx.x % kLruLanes;
+  const int b = blockIdx.x, c = blockIdx.y * kLruLanes + cl;
   const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
   if (n <= 0) return;
   const bool live = c < channels;
   if (positions[start] < 0) {                   // rows of a finished sequence: zeros, the state untouched
     if (live)
-      for (int i = warp; i < n; i += kLruWarps) out[(size_t)(start + i) * channels + c] = from_f<T>(0.f);
+      for (int i = sub; i < n; i += kLruSubs) out[(size_t)(start + i) * channels + c] = from_f<T>(0.f);
     return;
   }
   float* sp = state + (size_t)token_slot[start] * slot_stride + c;
   float S0 = live ? *sp : 0.f;
   const float sb = (side_bias && live) ? side_bias[c] : 0.f;
-  for (int base = 0; base < n; base += kLruWarps * kLruStretch) {
-    const int lo = base + warp * kLruStretch, hi = min(lo + kLruStretch, n);
+  for (int base = 0; base < n; base += kLruSubs * kLruStretch) {
+    const int lo = base + sub * kLruStretch, hi = min(lo + kLruStretch, n);
     float A = 1.f, B = 0.f;
     if (live) {
 #pragma unroll 8
@@ -319,11 +321,11 @@ lru_scan_wide_kernel(T* __restrict__ out, const float* __restrict__ a, const flo
         B = fmaf(av, B, x[at]);
       }
     }
-    A_s[warp][lane] = A;
-    B_s[warp][lane] = B;
+    A_s[sub][cl] = A;
+    B_s[sub][cl] = B;
     __syncthreads();
     float S = S0;
-    for (int w = 0; w < warp; ++w) S = fmaf(A_s[w][lane], S, B_s[w][lane]);
+    for (int w = 0; w < sub; ++w) S = fmaf(A_s[w][cl], S, B_s[w][cl]);
     if (live) {
 #pragma unroll 4
       for (int i = lo; i < hi; ++i) {
@@ -334,12 +336,15 @@ lru_scan_wide_kernel(T* __restrict__ out, const float* __restrict__ a, const flo
         out[row * channels + c] = from_f<T>(S * g);
       }
     }
-    float all = S0;
-    for (int w = 0; w < kLruWarps; ++w) all = fmaf(A_s[w][lane], all, B_s[w][lane]);
-    S0 = all;
+    if (base + kLruSubs * kLruStretch < n) {    // the state the next pass starts from
+      float all = S;
+      for (int w = sub + 1; w < kLruSubs; ++w) all = fmaf(A_s[w][cl], all, B_s[w][cl]);
+      S0 = all;
+    } else if (write_state && live && lo < n && hi == n) {
+      *sp = S;                                  // the stretch that ends the run leaves the state
+    }
     __syncthreads();                            // before the next pass overwrites A_s, B_s
   }
-  if (write_state && live && warp == 0) *sp = S0;
 }
 
 // a[t, h] = exp(-exp(a_log[h]) dt), b[t, h] = dt, dt = softplus(proj[t, col0 + h] + dt_bias[h]).
@@ -732,7 +737,7 @@ EK_EXPORT int ek_lru_gates(float* a, float* x, const float* u, int u_stride, con
     if (n_seqs <= 0) return 0;                                                                               \
     if (channels <= 0) return EK_ERR_ARG;                                                                    \
     if (max_new > 16) {              /* some sequence brings a stretch of tokens: the form for prompts */    \
-      dim3 wide(n_seqs, (channels + 31) / 32);                                                               \
+      dim3 wide(n_seqs, (channels + ek::kLruLanes - 1) / ek::kLruLanes);                                     \
       if (wide.y > 65535) return EK_ERR_ARG;                                                                 \
       return (int)ek::launch_pdl(ek::lru_scan_wide_kernel<T>, wide, dim3(ek::kLruWarps * 32), 0, stream,     \
                                  (T*)out, a, x, side, side_stride, side_col, side_bias, state,               \
