@@ -171,42 +171,58 @@ lru_gates_kernel(float* __restrict__ a_out, float* __restrict__ x_out, const flo
 
 // The same for few tokens (single tokens of a batch): a warp an output channel, its lanes spread over the
 // part's inputs, so that a step's few rows still give a block to every SM and every weight is read once, in
-// whole lines.  Weights here lie as stored, [part][out][in].  grid (channels / 8, token tiles of 8).
+// whole lines.  Weights here lie as stored, [part][out][in].  grid (parts * output tiles of 8, token tiles of 8);
+// a block stages its tokens' inputs of its part in shared memory once for its eight warps.
 constexpr int kLruFewTokens = 8;
 __global__ void __launch_bounds__(256)
 lru_gates_few_kernel(float* __restrict__ a_out, float* __restrict__ x_out, const float* __restrict__ u, int u_stride,
                      const float* __restrict__ w_a, const float* __restrict__ b_a, const float* __restrict__ w_i,
                      const float* __restrict__ b_i, const float* __restrict__ lam, float rate, int n_tokens, int parts,
                      int size) {
+  extern __shared__ __align__(16) float u_few[];              // [kLruFewTokens][size]
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int c = blockIdx.x * 8 + warp, R = parts * size;
-  if (c >= R) return;
-  const int p = c / size;
+  const int tiles = (size + 7) / 8;
+  const int p = blockIdx.x / tiles, o = (blockIdx.x % tiles) * 8 + warp;
+  const bool live = o < size;
+  const int c = p * size + (live ? o : 0), R = parts * size;
   const float* wa = w_a + (size_t)c * size;     // row c of the part's matrix: [out][in]
   const float* wi = w_i + (size_t)c * size;
   const int t0 = blockIdx.y * kLruFewTokens;
   const int nt = min(kLruFewTokens, n_tokens - t0);
+  float va[8], vi[8];                           // the weights do not depend on the kernel before: fetch, then wait
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int r = j * 32 + lane;
+    va[j] = (live && r < size) ? wa[r] : 0.f;
+    vi[j] = (live && r < size) ? wi[r] : 0.f;
+  }
+  pdl_wait();
+  for (int idx = threadIdx.x; idx < kLruFewTokens * size; idx += blockDim.x) {
+    const int tt = idx / size, r = idx % size;
+    u_few[idx] = tt < nt ? u[(size_t)(t0 + tt) * u_stride + p * size + r] : 0.f;
+  }
+  __syncthreads();
+  if (!live) return;
   float ra[kLruFewTokens], ri[kLruFewTokens];
 #pragma unroll
   for (int tt = 0; tt < kLruFewTokens; ++tt) ra[tt] = ri[tt] = 0.f;
-  float va[8], vi[8];                           // the weights do not depend on the kernel before: fetch, then wait
-  const int chunks = (size + 255) / 256;
-  for (int ch = 0; ch < chunks; ++ch) {
+  for (int r0 = 0; r0 < size; r0 += 256) {
+    if (r0 > 0) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int r = ch * 256 + j * 32 + lane;
-      va[j] = r < size ? wa[r] : 0.f;
-      vi[j] = r < size ? wi[r] : 0.f;
+      for (int j = 0; j < 8; ++j) {
+        const int r = r0 + j * 32 + lane;
+        va[j] = r < size ? wa[r] : 0.f;
+        vi[j] = r < size ? wi[r] : 0.f;
+      }
     }
-    if (ch == 0) pdl_wait();
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int r = ch * 256 + j * 32 + lane;
+      const int r = r0 + j * 32 + lane;
       if (r < size) {
 #pragma unroll
         for (int tt = 0; tt < kLruFewTokens; ++tt) {
-          const float x = tt < nt ? u[(size_t)(t0 + tt) * u_stride + p * size + r] : 0.f;
+          const float x = u_few[tt * size + r];
           ra[tt] = fmaf(va[j], x, ra[tt]);
           ri[tt] = fmaf(vi[j], x, ri[tt]);
         }
@@ -222,7 +238,7 @@ lru_gates_few_kernel(float* __restrict__ a_out, float* __restrict__ x_out, const
     const float log_a = -rate * softplus_f(lam[c]) * sigmoid_f(sa + (b_a ? b_a[c] : 0.f));
     const size_t at = (size_t)(t0 + lane) * R + c;
     a_out[at] = expf(log_a);
-    x_out[at] = sqrtf(-expm1f(2.f * log_a)) * sigmoid_f(si + (b_i ? b_i[c] : 0.f)) * u[(size_t)(t0 + lane) * u_stride + c];
+    x_out[at] = sqrtf(-expm1f(2.f * log_a)) * sigmoid_f(si + (b_i ? b_i[c] : 0.f)) * u_few[lane * size + o];
   }
 }
 
@@ -712,9 +728,14 @@ EK_EXPORT int ek_lru_gates(float* a, float* x, const float* u, int u_stride, con
   using namespace ek;
   if (n_tokens <= 0) return 0;
   if (parts <= 0 || size <= 0 || parts > 65535) return EK_ERR_ARG;
-  if (n_tokens <= 64 && w_a_rows && w_i_rows) {          // few tokens: a warp an output channel, weights as stored
-    dim3 grid((parts * size + 7) / 8, (n_tokens + kLruFewTokens - 1) / kLruFewTokens);
-    return (int)launch_pdl(lru_gates_few_kernel, grid, dim3(256), 0, stream, a, x, u, u_stride, w_a_rows, b_a,
+  const size_t few_smem = (size_t)kLruFewTokens * size * sizeof(float);
+  if (n_tokens <= 192 && w_a_rows && w_i_rows && few_smem <= 200 * 1024) {   // few tokens: a warp an output channel
+    if (few_smem > 40 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(lru_gates_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few_smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    dim3 grid(parts * ((size + 7) / 8), (n_tokens + kLruFewTokens - 1) / kLruFewTokens);
+    return (int)launch_pdl(lru_gates_few_kernel, grid, dim3(256), few_smem, stream, a, x, u, u_stride, w_a_rows, b_a,
                            w_i_rows, b_i, lam, rate, n_tokens, parts, size);
   }
   const size_t smem = (size_t)kLruTokens * ((size + 3) & ~3) * sizeof(float);

@@ -85,6 +85,11 @@ def build_musavik(cfg: MusavikConfig) -> ModelSpec:
         pair = isinstance(cfg.layers[i].mixer, SideBySideConfig)
         schedule.append(RunSpec(i, entries, mix_input=starts_pass, more_caches=(entries + 1,) if pair else ()))
         entries += 2 if pair else 1
+    # (a file may keep the tensors of an input mix or a pair table that its configuration does not use)
+    if cfg.loop is None:
+        ignorable.append("loop.in")
+    if cfg.pair_table is None:
+        ignorable.append("bigram")
     pairs = None
     if cfg.pair_table is not None:
         t = cfg.pair_table

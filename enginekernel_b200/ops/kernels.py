@@ -1564,7 +1564,7 @@ def lru_gates(a, x, u, w_a, b_a, w_i, b_i, lam, rate, n_tokens, parts, size, w_a
     """Gates of a gated linear recurrence over ``parts * size`` channels: r = sigmoid(W_a[p] u_p + b_a),
     i = sigmoid(W_i[p] u_p + b_i) per part p; a = exp(-rate * r * softplus(lam)), x = sqrt(1 - a^2) * i * u.
     ``w_a``, ``w_i`` [parts, in, out] (transposed), everything 32-bit.  ``w_a_rows``, ``w_i_rows``: the same
-    matrices [parts, out, in]; with them steps of at most 64 tokens run a warp per output channel."""
+    matrices [parts, out, in]; with them steps of at most 192 tokens run a warp per output channel."""
     _need_cuda(a, x, u, w_a, b_a, w_i, b_i, lam, w_a_rows, w_i_rows)
     _need_f32("lru_gates", a, x, u, w_a, b_a, w_i, b_i, lam, w_a_rows, w_i_rows)
     for t in (w_a_rows, w_i_rows):

@@ -142,10 +142,10 @@ def test_convolution_with_a_bias_on_its_input(channels, taps):
         at += m
 
 
-@pytest.mark.parametrize("parts,size", [(1, 64), (5, 16), (2, 30), (3, 200), (4, 129)])
+@pytest.mark.parametrize("parts,size", [(1, 64), (5, 16), (2, 30), (3, 200), (4, 129), (2, 300)])
 def test_gates_of_the_linear_recurrence(parts, size):
     k = K()
-    n, width = 37, parts * size
+    n, width = 237, parts * size
     u = rnd(n, width + 5, seed=1)
     wa, wi = rnd(parts, size, size, seed=2, scale=2 / math.sqrt(size)), rnd(parts, size, size, seed=3, scale=2 / math.sqrt(size))
     ba, bi, lam = rnd(parts, size, seed=4, scale=0.3), rnd(parts, size, seed=5, scale=0.3), rnd(width, seed=6, scale=1.5) - 2
@@ -156,7 +156,7 @@ def test_gates_of_the_linear_recurrence(parts, size):
     wat, wit = wa.transpose(1, 2).contiguous(), wi.transpose(1, 2).contiguous()
     # a tile of tokens a block (prompts), and a warp an output channel (steps of few tokens, weights as stored)
     for rows in ({}, {"w_a_rows": wa.contiguous(), "w_i_rows": wi.contiguous()}):
-        for m in (n, 3, 1):
+        for m in (n, 37, 3, 1):
             a, x = torch.empty(m, width, device=DEV), torch.empty(m, width, device=DEV)
             k.lru_gates(a, x, u[:m], wat, ba.reshape(-1), wit, bi.reshape(-1), lam, 8.0, m, parts, size, **rows)
             assert rel(a, torch.exp(log_a)[:m]) <= 1e-5
