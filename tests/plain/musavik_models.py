@@ -79,9 +79,9 @@ ODD = config(100, 89, [
     eps=1e-4, embedding_scale=1.5, pairs=(13, 1000, 999), loop=(2, 3, 1))
 # key size 128; a loop in the middle; pairs only
 WIDE = config(256, 301, [
-    (parallel(left(8, 4, 128, 64, 64, 33, keep_first=9, base=5e5), right(4, 2, 64, 32, 4), 0.8, 0.5), dense(96)),
+    (parallel(left(8, 4, 128, 64, 64, 33, keep_first=9, base=2e5), right(4, 2, 64, 32, 4), 0.6, 0.4), dense(96)),
     (parallel(left(4, 1, 64, 128, 16, 130, keep_first=1), right(2, 2, 128, 64, 2), 1.0, 1.0), dense(64)),
-    (rglru(192, 2, 4), dense(128))], embedding_scale=3.0, pairs=(509, 3, 5), loop=(1, 2, 2))
+    (rglru(192, 2, 4), dense(128))], embedding_scale=3.0, pairs=(499, 3, 5), loop=(1, 2, 2))
 
 SHAPES = {"early": EARLY, "flat": FLAT, "odd": ODD, "wide": WIDE}
 
